@@ -310,6 +310,84 @@ int p3_mega_pack(const void* W, void* out, int kind, int N, int K, int n_heads, 
 int p3_decode_mega_ctas(void);
 int p3_decode_mega(const p3_mega_args* args, cudaStream_t st);
 
+/* ------------------------------------------------------------------------------------------------------------------------
+ * Decoders with an fp32 residual stream, a ragged token batch and a page pool shared by all live sequences (Tagenex and any
+ * design built from the same parts). "act" tensors are bf16, or fp32 in the all-fp32 serving mode (act_f32 / cache_f32 = 1);
+ * norms, softmax, router and residual sums are fp32 in both. One K pool and one V pool per layer:
+ * [page][kv head][P3_PAGE_TOKENS][dim | vdim]; block_table int32 [sequence slot][bt_stride] of page ids. */
+
+/* out[M,N] = X[M,K] W[N,K]^T + bias for any sizes / strides / alignment; X and W both fp32 (FMA pipes, no TF32) or both bf16
+ * (mma.sync when K, ldx, ldw are multiples of 8 and the bases 16-byte aligned, else FMA); fp32 accumulation in ascending k.
+ * x_rows (may be NULL): row r reads X[x_rows[r] / x_row_div]. seg_offsets (device int32 [n_groups + 1], may be NULL): rows
+ * [seg[g], seg[g+1]) multiply with W + g * w_group_stride and add bias + g * bias_group_stride (grouped expert product; M is
+ * then the total row count = seg[n_groups]). bias fp32 or NULL. */
+typedef struct {
+    const void* X; int64_t ldx; int32_t x_f32; const int32_t* x_rows; int32_t x_row_div;
+    const void* W; int64_t ldw; int32_t w_f32; int64_t w_group_stride;
+    const float* bias; int64_t bias_group_stride;
+    void* out; int64_t ldo; int32_t out_f32;
+    int64_t M; int32_t N, K;
+    const int32_t* seg_offsets; int32_t n_groups;
+    int32_t force_fma;           /* tests: bf16 operands on the FMA kernel */
+} p3_gemm_any_args;
+int p3_gemm_any(const p3_gemm_any_args* args, cudaStream_t st);
+
+/* x fp32 [T,W] = table[ids] (bf16 table); x_act (may be NULL) receives the same rows in the activation type */
+int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
+                      cudaStream_t st);
+/* norm on a sublayer's OUTPUT: x += y / sqrt(mean(y^2) + eps) * gain; x_act (may be NULL) = the new x in the activation type */
+int p3_postnorm_residual(const float* y, int64_t ldy, const float* gain, float* x, void* x_act, int act_f32, int64_t T, int W,
+                         float eps, cudaStream_t st);
+/* out[r] = rms_norm(x[rows[r]]) * gain (rows NULL: r itself): the model's last norm, only for the rows whose logits are wanted */
+int p3_rmsnorm_rows_f32(const float* x, const int32_t* rows, const float* gain, void* out, int out_f32, int64_t R, int W, float eps,
+                        cudaStream_t st);
+
+/* After the fused q|k|v|gate projection (proj fp32 [T, ld_proj], column offsets *_off): per-head RMS norm of q and k with gains
+ * shared by all heads, q -> q_out (act), k -> K pool; v_mode 0: v -> V pool, 1: also kept in v_first (fp32 [T, n_kv * vdim]),
+ * 2: v <- (1 - v_lambda) v + v_lambda v_first before it is cached; gate_out (may be NULL) fp32 [T, n_heads] = sigmoid(gate
+ * logits). Token t of the batch belongs to sequence slot tok_slot[t] at position tok_pos[t]. */
+typedef struct {
+    const float* proj; int64_t ld_proj; int32_t q_off, k_off, v_off, g_off;
+    int32_t n_heads, n_kv, dim, vdim;
+    const float* q_gain; const float* k_gain; float eps;
+    float* v_first; int32_t v_mode; float v_lambda;
+    void* q_out; int64_t ld_q; float* gate_out;
+    void* k_pool; void* v_pool; const int32_t* block_table; int32_t bt_stride;
+    const int32_t* tok_slot; const int32_t* tok_pos; int32_t T;
+    int32_t act_f32, cache_f32;
+} p3_qkv_post_args;
+int p3_qkv_post(const p3_qkv_post_args* args, cudaStream_t st);
+
+/* Sliding-window attention with sink and distance penalty over the page pools (csrc/attention_window.cu). tiles = int32 x 4 per
+ * CTA row: {first batch row, number of query rows (<= 32; decode: 1), sequence slot, position of the first row}. window 0 = no
+ * limit. sink fp32 [n_heads] or NULL; penalty fp32 [n_heads][n_penalty] (value at distance i - j, clamped to the table) or NULL;
+ * gate fp32 [T, n_heads] or NULL multiplies the head outputs. out (act) [T, ld_out], head h at column h * vdim. */
+typedef struct {
+    const void* q; int64_t ld_q;
+    const void* k_pool; const void* v_pool; const int32_t* block_table; int32_t bt_stride;
+    const float* sink; const float* penalty; int32_t n_penalty; const float* gate;
+    void* out; int64_t ld_out;
+    int32_t n_heads, n_kv, dim, vdim; float scale; int32_t window;
+    int32_t act_f32, cache_f32;
+    const int32_t* tiles; int32_t n_tiles;
+} p3_attn_window_args;
+int p3_attn_window_prefill(const p3_attn_window_args* args, cudaStream_t st);
+int p3_attn_window_decode(const p3_attn_window_args* args, cudaStream_t st);
+
+/* out (act) [R, F] = g' * sigmoid(alpha g') * (u' + 1), g' = min(gu[:, :F], limit), u' = clamp(gu[:, F:2F], -limit, limit) */
+int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, float limit, float alpha,
+                   const int32_t* n_rows_dev, cudaStream_t st);
+/* router: z = Wr x + br in fp32; the `top` largest (ties: lower index) -> ids [T, top]; wts = softmax over the chosen logits */
+int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* br, int T, int W, int E, int top, int32_t* ids,
+                   float* wts, cudaStream_t st);
+/* stable sort of the n = T * top (token, choice) pairs by expert: seg [E + 1], order [n] (sorted row -> pair), where [n] (pair ->
+ * sorted row); feeds p3_gemm_any's segments and p3_moe_combine */
+int p3_moe_sort(const int32_t* ids, int n, int E, int32_t* seg, int32_t* order, int32_t* where, cudaStream_t st);
+int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const float* wts, int top, float* out, int64_t T, int W,
+                   cudaStream_t st);
+/* pen[h][i] = r1[h] * ln(1 + r2[h] * i), i < n */
+int p3_distance_penalty_table(const float* r1, const float* r2, float* pen, int H, int n, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

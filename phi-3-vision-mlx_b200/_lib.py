@@ -8,7 +8,25 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get('P3_LIB') or os.path.join(_HERE, 'libphi3b200.so')     # P3_LIB: tuning builds (tools/), same ABI
+# Two builds of the same sources: the full library, and the language-model subset (no Phi-3 attention / vision / quantisation
+# kernels) that a fresh checkout compiles when only an engine model is served. The full one wins when both exist.
+FULL_PATH = os.path.join(_HERE, 'libphi3b200.so')
+LM_PATH = os.path.join(_HERE, 'libphi3b200_lm.so')
+LIB_PATH = os.environ.get('P3_LIB') or FULL_PATH                               # P3_LIB: tuning builds (tools/), same ABI
+
+
+def ensure_built(full=True):
+    """compile the CUDA library if no usable build is there (make -C csrc; sm_100a, needs nvcc): the full library, or with
+    full=False just the subset the engine models use. Existing builds are never rebuilt here."""
+    import subprocess
+    if os.environ.get('P3_LIB') or os.path.exists(FULL_PATH) or (not full and os.path.exists(LM_PATH)):
+        return
+    env = dict(os.environ)
+    if not any(os.path.exists(os.path.join(d, 'nvcc')) for d in env.get('PATH', '').split(os.pathsep) if d):
+        env['PATH'] = env.get('PATH', '') + os.pathsep + '/usr/local/cuda/bin'
+    subprocess.check_call(['make', '-C', os.path.join(_HERE, 'csrc'), '-j8', 'all' if full else 'lm'], env=env,
+                          stdout=subprocess.DEVNULL)
+
 
 EPI_NONE, EPI_QGELU, EPI_GELU, EPI_RESIDUAL, EPI_SWIGLU, EPI_F32, EPI_RESIDUAL_F32 = range(7)
 EPI_ROPE_KV = 8
@@ -44,7 +62,17 @@ _SIGS = {
     'p3_row_sumsq': [_p, _l, _p, _l, _i, _p],
     'p3_rope_table': [_p, _l, _i, _p, _p, _p, _i, _i, _i, _f, _p],
     'p3_embed_gather_xg': [_p, _p, _p, _l, _i, _i, _p, _p, _p, _p],
+    # decoders with an fp32 residual stream over a shared page pool (csrc/seq_ops.cu)
+    'p3_embed_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _i, _p],
+    'p3_postnorm_residual': [_p, _l, _p, _p, _p, _i, _l, _i, _f, _p],
+    'p3_rmsnorm_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _f, _p],
+    'p3_glu_clamped': [_p, _l, _p, _l, _i, _l, _i, _f, _f, _p, _p],
+    'p3_router_topk': [_p, _l, _i, _p, _p, _i, _i, _i, _i, _p, _p, _p],
+    'p3_moe_sort': [_p, _i, _i, _p, _p, _p, _p],
+    'p3_moe_combine': [_p, _l, _p, _p, _i, _p, _l, _i, _p],
+    'p3_distance_penalty_table': [_p, _p, _p, _i, _i, _p],
 }
+_STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode']
 
 _lib = None
 launches = 0          # number of p3_* kernel-launching calls issued (bench.py reports it)
@@ -52,19 +80,31 @@ launches = 0          # number of p3_* kernel-launching calls issued (bench.py r
 
 def exported_symbols():
     return sorted(list(_SIGS) + ['p3_last_error', 'p3_version', 'p3_attention_decode_workspace', 'p3_decode_mega',
-                                 'p3_decode_mega_ctas', 'p3_gemm_fused', 'p3_gemm_plan_weights', 'p3_gemm_skinny_x', 'p3_trace_set', 'p3_trace_count'])
+                                 'p3_decode_mega_ctas', 'p3_gemm_fused', 'p3_gemm_plan_weights', 'p3_gemm_skinny_x', 'p3_trace_set', 'p3_trace_count']
+                  + _STRUCT_ENTRIES)
 
 
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = LIB_PATH if os.path.exists(LIB_PATH) else LM_PATH
+        if not os.path.exists(path):
             raise RuntimeError(f'{LIB_PATH} is missing: the CUDA extension must be built (no CPU fallback exists). '
                                'Run __graft_entry__.build().')
-        L = C.CDLL(LIB_PATH)
+        L = C.CDLL(path)
+        lm_only = not hasattr(L, 'p3_attention_decode')
         for name, sig in _SIGS.items():
+            if lm_only and not hasattr(L, name):
+                continue                                     # subset build: calling a missing entry raises AttributeError
             fn = getattr(L, name)
             fn.argtypes, fn.restype = sig, C.c_int
+        if lm_only:
+            for name in _STRUCT_ENTRIES:
+                getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
+            L.p3_last_error.restype = C.c_char_p
+            L.p3_version.restype = C.c_int
+            _lib = L
+            return _lib
         L.p3_last_error.restype = C.c_char_p
         L.p3_version.restype = C.c_int
         L.p3_attention_decode_workspace.argtypes = [_i, _i, _i, _i, _i]
@@ -76,6 +116,8 @@ def lib():
         L.p3_gemm_skinny_x.argtypes, L.p3_gemm_skinny_x.restype = [_p, _p], C.c_int        # (const p3_skinny_args*, stream)
         L.p3_trace_set.argtypes, L.p3_trace_set.restype = [_p, C.c_int], C.c_int           # diagnostics (tools/chain_trace.py)
         L.p3_trace_count.argtypes, L.p3_trace_count.restype = [], C.c_int
+        for name in _STRUCT_ENTRIES:                                                        # (const args*, stream)
+            getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
         _lib = L
     return _lib
 
@@ -139,3 +181,31 @@ class WeightPlan:
         rc = lib().p3_gemm_plan_weights(w.data_ptr(), w.stride(0), w.shape[0], w.shape[1], self.addr)
         if rc != 0:
             raise RuntimeError(f'p3_gemm_plan_weights failed ({rc}): {lib().p3_last_error().decode()}')
+
+
+class GemmAnyArgs(C.Structure):
+    """p3_gemm_any_args (include/phi3_b200.h)"""
+    _fields_ = [('X', _p), ('ldx', _l), ('x_f32', C.c_int32), ('x_rows', _p), ('x_row_div', C.c_int32),
+                ('W', _p), ('ldw', _l), ('w_f32', C.c_int32), ('w_group_stride', _l),
+                ('bias', _p), ('bias_group_stride', _l), ('out', _p), ('ldo', _l), ('out_f32', C.c_int32),
+                ('M', _l), ('N', C.c_int32), ('K', C.c_int32), ('seg_offsets', _p), ('n_groups', C.c_int32),
+                ('force_fma', C.c_int32)]
+
+
+class QkvPostArgs(C.Structure):
+    """p3_qkv_post_args (include/phi3_b200.h)"""
+    _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('k_off', C.c_int32), ('v_off', C.c_int32), ('g_off', C.c_int32),
+                ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32),
+                ('q_gain', _p), ('k_gain', _p), ('eps', C.c_float),
+                ('v_first', _p), ('v_mode', C.c_int32), ('v_lambda', C.c_float),
+                ('q_out', _p), ('ld_q', _l), ('gate_out', _p),
+                ('k_pool', _p), ('v_pool', _p), ('block_table', _p), ('bt_stride', C.c_int32),
+                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]
+
+
+class AttnWindowArgs(C.Structure):
+    """p3_attn_window_args (include/phi3_b200.h)"""
+    _fields_ = [('q', _p), ('ld_q', _l), ('k_pool', _p), ('v_pool', _p), ('block_table', _p), ('bt_stride', C.c_int32),
+                ('sink', _p), ('penalty', _p), ('n_penalty', C.c_int32), ('gate', _p), ('out', _p), ('ld_out', _l),
+                ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('scale', C.c_float),
+                ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32)]

@@ -68,3 +68,73 @@ def with_overrides(cfg, **kw):
     for k, v in kw.items():
         setattr(c, k, v)
     return c
+
+
+# ------------------------------------------------------------------------------------------------ Tagenex
+class TagenexConfig:
+    """config.json of a Tagenex checkpoint: {"architecture": "Tagenex", "vocab", "width", "norm": {"eps"}, "layers": [...]}.
+    Every layer entry has "type" (the mixer kind; "attention"), "mixer" (heads, kv_heads, dim, vdim, scale, v_mix,
+    mask: {size} or absent = no window) and "mlp": null | {"kind": "dense", ff, limit} | {"kind": "moe", expert: {ff, limit},
+    router: {experts, top}}. Nothing is assumed equal between layers except the value shape of the layers that mix values."""
+    GLU_ALPHA = 1.702          # slope of the sigmoid in the gated activation: fixed by the design
+
+    def __init__(self, d):
+        self.raw = d
+        self.architecture = d.get('architecture', 'Tagenex')
+        self.architectures = [self.architecture]
+        self.vocab_size, self.width = int(d['vocab']), int(d['width'])
+        self.eps = float(d['norm']['eps'])
+        self.layers = []
+        first_mix = None
+        for i, lc in enumerate(d['layers']):
+            if lc.get('type', 'attention') != 'attention':
+                raise NotImplementedError(f"layer {i}: mixer type {lc.get('type')!r} is not part of this design")
+            m = lc['mixer']
+            mixer = SimpleNamespace(kind='attention', heads=int(m['heads']), kv_heads=int(m.get('kv_heads', m['heads'])),
+                                    dim=int(m['dim']), vdim=int(m.get('vdim', m['dim'])), scale=float(m['scale']),
+                                    window=int((m.get('mask') or {}).get('size') or 0), v_mix=bool(m.get('v_mix', False)),
+                                    v_role='none')
+            if mixer.heads % mixer.kv_heads:
+                raise ValueError(f'layer {i}: heads must be a multiple of kv_heads')
+            if mixer.v_mix:
+                if first_mix is None:
+                    first_mix, mixer.v_role = mixer, 'source'
+                else:
+                    if (mixer.kv_heads, mixer.vdim) != (first_mix.kv_heads, first_mix.vdim):
+                        raise ValueError(f'layer {i}: value mixing needs the value shape of the first mixing layer')
+                    mixer.v_role = 'mix'
+            f = lc.get('mlp')
+            if f is None:
+                ff = None
+            elif f['kind'] == 'dense':
+                ff = SimpleNamespace(kind='dense', ff=int(f['ff']), limit=float(f['limit']))
+            elif f['kind'] == 'moe':
+                ff = SimpleNamespace(kind='moe', ff=int(f['expert']['ff']), limit=float(f['expert']['limit']),
+                                     experts=int(f['router']['experts']), top=int(f['router']['top']))
+                if not 1 <= ff.top <= ff.experts:
+                    raise ValueError(f'layer {i}: top must be in [1, experts]')
+            else:
+                raise NotImplementedError(f"layer {i}: feed-forward kind {f['kind']!r}")
+            self.layers.append(SimpleNamespace(mixer=mixer, ff=ff))
+        self.num_hidden_layers = len(self.layers)
+
+    def kv_layout(self):
+        """per layer (kv heads, key size, value size): what the page pool allocates"""
+        return [(l.mixer.kv_heads, l.mixer.dim, l.mixer.vdim) for l in self.layers]
+
+
+def tiny_tagenex(width=96, vocab=300, layers=None, eps=1e-5):
+    """A small Tagenex config dict for tests (sizes deliberately unequal: dim != vdim, heads != kv_heads, windows that differ
+    between layers, one layer without a window, one without a feed-forward, one that does not mix values)."""
+    att = lambda heads, kv, dim, vdim, win, mix, scale=None: {
+        'type': 'attention',
+        'mixer': dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=scale or dim ** -0.5, v_mix=mix,
+                      **({'mask': {'size': win}} if win else {}))}
+    dense = lambda ff, lim=2.0: {'kind': 'dense', 'ff': ff, 'limit': lim}
+    moe = lambda ff, e, top, lim=2.0: {'kind': 'moe', 'expert': {'ff': ff, 'limit': lim}, 'router': {'experts': e, 'top': top}}
+    if layers is None:
+        layers = [dict(att(6, 3, 40, 24, 50, True), mlp=dense(136)),
+                  dict(att(4, 1, 48, 24, 0, False), mlp=moe(56, 5, 2)),
+                  dict(att(6, 3, 24, 24, 33, True), mlp=None),
+                  dict(att(3, 3, 32, 24, 100, True), mlp=moe(40, 3, 3))]
+    return {'architecture': 'Tagenex', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'layers': layers}

@@ -1,0 +1,196 @@
+// p3_gemm_any: out[M,N] = X[M,K] * W[N,K]^T (+ bias) for ANY sizes, strides and alignments, operands fp32 or bf16, fp32
+// accumulation in ascending k (one FMA chain per output element, so a row's result does not depend on which other rows share
+// the launch). Two extras make it the mixture-of-experts workhorse: the rows of X can be gathered through an index list, and
+// the rows can be cut into segments that each multiply with their own weight matrix (device-side segment offsets, so the host
+// never learns how many tokens an expert received).
+//
+// fp32 operands run on the FMA pipes (this is the "true 32-bit" path: no TF32). bf16 operands of aligned shapes run on the
+// tensor cores through mma.sync m16n8k16 (fp32 accumulators); the dense bf16 projections with K % 8 == 0 go to the tcgen05
+// kernel (p3_gemm) instead — this file is what is left: grouped expert products, fp32, and shapes p3_gemm does not take.
+#include "common.cuh"
+#include "../../include/phi3_b200.h"
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 16;
+
+struct AnyP {
+    const void* X; int64_t ldx; const int32_t* x_rows; int x_row_div;
+    const void* W; int64_t ldw; int64_t w_gstride;
+    const float* bias; int64_t bias_gstride;
+    void* out; int64_t ldo;
+    int64_t M; int N, K;
+    const int32_t* seg; int n_groups;
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return __ldg(p); }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// which (group, first row, end row) does m-tile `tile` cover? Groups are walked in order; a launch has at most
+// ceil(M / BM) + n_groups tiles, surplus CTAs leave.
+__device__ __forceinline__ bool find_tile(const AnyP& p, int tile, int& g, int64_t& m0, int64_t& m1) {
+    if (!p.seg) { g = 0; m0 = (int64_t)tile * BM; m1 = p.M; return m0 < m1; }
+    int t = tile;
+    for (int e = 0; e < p.n_groups; e++) {
+        const int a = p.seg[e], b = p.seg[e + 1], nt = (b - a + BM - 1) / BM;
+        if (t < nt) { g = e; m0 = a + (int64_t)t * BM; m1 = b; return true; }
+        t -= nt;
+    }
+    return false;
+}
+
+template <typename XT, typename WT, typename OT>
+__global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
+    __shared__ __align__(16) float As[BK][BM + 4];
+    __shared__ __align__(16) float Bs[BK][BN + 4];
+    int g; int64_t m0, m1;
+    if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
+    const int n0 = blockIdx.y * BN, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const XT* X = (const XT*)p.X;
+    const WT* W = (const WT*)p.W + (size_t)g * p.w_gstride;
+    // this thread stages row (tid / 4) of each tile, k = (tid % 4) * 4 .. + 3
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    const int64_t am = m0 + lr;
+    const XT* arow = nullptr;
+    if (am < m1) arow = X + (size_t)(p.x_rows ? p.x_rows[am] / p.x_row_div : am) * p.ldx;
+    const WT* brow = (n0 + lr < p.N) ? W + (size_t)(n0 + lr) * p.ldw : nullptr;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < p.K; k0 += BK) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int k = k0 + lk + j;
+            As[lk + j][lr] = (arow && k < p.K) ? ldf(arow + k) : 0.f;
+            Bs[lk + j][lr] = (brow && k < p.K) ? ldf(brow + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
+    OT* out = (OT*)p.out;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int64_t m = m0 + ty * 4 + i;
+        if (m >= m1) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < p.N) stf(out + (size_t)m * p.ldo + n, acc[i][j] + (bias ? bias[n] : 0.f));
+        }
+    }
+}
+
+// bf16 x bf16 on the tensor cores: 64 x 64 tile, 4 warps (2 x 2), each warp 32 x 32 = 2 x 4 MMAs of m16n8k16 per 16-wide k
+// step; operands staged through shared memory as bf16 (row-major [row][k], 16-byte chunks, K % 8 == 0 and 16-byte aligned rows
+// required by the launcher). Same tile walk, gather and segment logic as the FMA kernel.
+constexpr int TK = 32;                                     // k elements per stage
+template <typename OT>
+__global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
+    __shared__ __align__(16) bf16 As[BM][TK + 8];
+    __shared__ __align__(16) bf16 Bs[BN][TK + 8];
+    int g; int64_t m0, m1;
+    if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
+    const int n0 = blockIdx.y * BN, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const bf16* X = (const bf16*)p.X;
+    const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride;
+    // staging: 64 rows x 4 chunks of 8 elements = 256 chunks per operand, 2 per thread
+    const bf16* arow[2]; const bf16* brow[2]; int srow[2], schunk[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int c = tid + j * 128;
+        srow[j] = c >> 2; schunk[j] = (c & 3) * 8;
+        const int64_t am = m0 + srow[j];
+        arow[j] = (am < m1) ? X + (size_t)(p.x_rows ? p.x_rows[am] / p.x_row_div : am) * p.ldx : nullptr;
+        brow[j] = (n0 + srow[j] < p.N) ? W + (size_t)(n0 + srow[j]) * p.ldw : nullptr;
+    }
+    float acc[2][4][4] = {};
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int k0 = 0; k0 < p.K; k0 += TK) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int k = k0 + schunk[j];
+            const bool in = k < p.K;                       // K % 8 == 0: a chunk is inside or outside as a whole
+            *reinterpret_cast<uint4*>(&As[srow[j]][schunk[j]]) = (arow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(arow[j] + k)) : zero;
+            *reinterpret_cast<uint4*>(&Bs[srow[j]][schunk[j]]) = (brow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(brow[j] + k)) : zero;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; kk += 16) {
+            uint32_t a[2][4], b[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int r = wm + i * 16 + (lane >> 2), c = kk + (lane & 3) * 2;
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][c]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][c + 8]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int r = wn + j * 8 + (lane >> 2), c = kk + (lane & 3) * 2;
+                b[j][0] = *reinterpret_cast<const uint32_t*>(&Bs[r][c]);
+                b[j][1] = *reinterpret_cast<const uint32_t*>(&Bs[r][c + 8]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) mma_bf16_16816(acc[i][j], a[i], b[j][0], b[j][1]);
+        }
+        __syncthreads();
+    }
+    const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
+    OT* out = (OT*)p.out;
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int64_t m = m0 + wm + i * 16 + (lane >> 2) + (e >> 1) * 8;
+                const int n = n0 + wn + j * 8 + (lane & 3) * 2 + (e & 1);
+                if (m < m1 && n < p.N) stf(out + (size_t)m * p.ldo + n, acc[i][j][e] + (bias ? bias[n] : 0.f));
+            }
+}
+}  // namespace
+
+extern "C" int p3_gemm_any(const p3_gemm_any_args* a, cudaStream_t st) {
+    P3_CHECK_ARG(a && a->X && a->W && a->out, "gemm_any: null operand");
+    P3_CHECK_ARG(a->M >= 0 && a->N >= 1 && a->K >= 1 && a->M < (1ll << 30), "gemm_any: bad sizes");
+    P3_CHECK_ARG(!a->seg_offsets || a->n_groups >= 1, "gemm_any: segments need n_groups >= 1");
+    P3_CHECK_ARG(!a->x_rows || a->x_row_div >= 1, "gemm_any: gather needs x_row_div >= 1");
+    P3_CHECK_ARG(a->x_f32 == a->w_f32, "gemm_any: X and W must have the same element type");
+    if (a->M == 0) return 0;
+    AnyP p{a->X, a->ldx, a->x_rows, a->x_row_div, a->W, a->ldw, a->w_group_stride, a->bias, a->bias_group_stride,
+           a->out, a->ldo, a->M, a->N, a->K, a->seg_offsets, a->seg_offsets ? a->n_groups : 1};
+    const unsigned mt = (unsigned)((a->M + BM - 1) / BM) + (a->seg_offsets ? (unsigned)a->n_groups : 0u);
+    const dim3 grid(mt, (unsigned)((a->N + BN - 1) / BN));
+    if (a->x_f32) {
+        if (a->out_f32) gemm_any_fma_kernel<float, float, float><<<grid, 256, 0, st>>>(p);
+        else gemm_any_fma_kernel<float, float, bf16><<<grid, 256, 0, st>>>(p);
+    } else {
+        const bool tc = a->K % 8 == 0 && a->ldx % 8 == 0 && a->ldw % 8 == 0 && a->w_group_stride % 8 == 0 &&
+                        ((uintptr_t)a->X & 15) == 0 && ((uintptr_t)a->W & 15) == 0 && !a->force_fma;
+        if (tc) {
+            if (a->out_f32) gemm_any_mma_kernel<float><<<grid, 128, 0, st>>>(p);
+            else gemm_any_mma_kernel<bf16><<<grid, 128, 0, st>>>(p);
+        } else {
+            if (a->out_f32) gemm_any_fma_kernel<bf16, bf16, float><<<grid, 256, 0, st>>>(p);
+            else gemm_any_fma_kernel<bf16, bf16, bf16><<<grid, 256, 0, st>>>(p);
+        }
+    }
+    P3_CHECK_LAUNCH("gemm_any");
+    return 0;
+}

@@ -1,0 +1,308 @@
+// Row kernels of decoders that keep the residual stream in fp32 and run a ragged token batch (several sequences, each with its
+// own number of new tokens) against a paged cache: embedding into fp32, RMS norm of a sublayer's OUTPUT fused with the residual
+// add, per-head query/key RMS norm fused with value mixing, the output-gate sigmoid and the paged K/V write, the clamped
+// gated-linear activation, the mixture-of-experts router (logits, top-k, softmax over the chosen), the expert sort and the
+// weighted combine, and the distance-penalty table of the biased attention. Everything here is fp32 arithmetic; only the
+// storage type of activations ("act": bf16 or fp32) and of the cache differs between the serving mode and the all-fp32 mode.
+#include "common.cuh"
+#include "../../include/phi3_b200.h"
+
+namespace {
+template <typename T> __device__ __forceinline__ float ldv(const T* p);
+template <> __device__ __forceinline__ float ldv<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldv<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stv(T* p, float v);
+template <> __device__ __forceinline__ void stv<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stv<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// sum over a CTA of up to 1024 threads; every thread gets the total. The order of the additions is fixed by the thread
+// layout alone, so a row's statistic does not depend on the batch it is in.
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += sh[i];
+    return t;
+}
+
+// ---------------------------------------------------------------- embedding -> fp32 residual (+ activation copy)
+template <typename AT>
+__global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ x,
+                                  AT* __restrict__ xa, int W, int vocab) {
+    const int64_t t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = __bfloat162float(table[(size_t)id * W + i]);
+        x[(size_t)t * W + i] = v;
+        if (xa) stv(xa + (size_t)t * W + i, v);
+    }
+}
+
+// ---------------------------------------------------------------- x += rms_norm(y) * gain ; activation copy of the new x
+template <typename AT>
+__global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gain,
+                                         float* __restrict__ x, AT* __restrict__ xa, int W, float eps) {
+    __shared__ float sh[32];
+    const int64_t t = blockIdx.x;
+    const float* yr = y + (size_t)t * ldy;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, sh);
+    const float r = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = x[(size_t)t * W + i] + yr[i] * r * gain[i];
+        x[(size_t)t * W + i] = v;
+        if (xa) stv(xa + (size_t)t * W + i, v);
+    }
+}
+
+// ---------------------------------------------------------------- out[r] = rms_norm(x[rows[r]]) * gain   (final norm of chosen rows)
+template <typename AT>
+__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ gain,
+                                    AT* __restrict__ out, int W, float eps) {
+    __shared__ float sh[32];
+    const int64_t r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, sh);
+    const float s = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) stv(out + (size_t)r * W + i, xr[i] * s * gain[i]);
+}
+
+// ---------------------------------------------------------------- per-head q/k norm + value mixing + gate + paged K/V write
+// One CTA per token, one warp per head job: H query heads, G key heads, G value heads, then the H gate logits.
+template <typename AT, typename CT>
+__global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* pr = a.proj + (size_t)t * a.ld_proj;
+    const int slot = a.tok_slot[t], pos = a.tok_pos[t];
+    const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
+    const int H = a.n_heads, G = a.n_kv, d = a.dim, dv = a.vdim;
+    for (int job = warp; job < H + 2 * G; job += nw) {
+        if (job < H + G) {                                   // query or key head: RMS norm over its d numbers, shared gain
+            const bool isq = job < H;
+            const int h = isq ? job : job - H;
+            const float* src = pr + (isq ? a.q_off : a.k_off) + (size_t)h * d;
+            const float* gain = isq ? a.q_gain : a.k_gain;
+            float ss = 0.f;
+            for (int i = lane; i < d; i += 32) ss = fmaf(src[i], src[i], ss);
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)d + a.eps);
+            if (isq) {
+                AT* dst = (AT*)a.q_out + (size_t)t * a.ld_q + (size_t)h * d;
+                for (int i = lane; i < d; i += 32) stv(dst + i, src[i] * r * gain[i]);
+            } else {
+                CT* dst = (CT*)a.k_pool + (((size_t)page * G + h) * P3_PAGE + off) * d;
+                for (int i = lane; i < d; i += 32) stv(dst + i, src[i] * r * gain[i]);
+            }
+        } else {                                             // value head: v, or (1 - lam) v + lam v_first; the mixed v is cached
+            const int h = job - H - G;
+            const float* src = pr + a.v_off + (size_t)h * dv;
+            float* vf = a.v_first ? a.v_first + (size_t)t * G * dv + (size_t)h * dv : nullptr;
+            CT* dst = (CT*)a.v_pool + (((size_t)page * G + h) * P3_PAGE + off) * dv;
+            for (int i = lane; i < dv; i += 32) {
+                float v = src[i];
+                if (a.v_mode == 1) vf[i] = v;
+                else if (a.v_mode == 2) v = (1.0f - a.v_lambda) * v + a.v_lambda * vf[i];
+                stv(dst + i, v);
+            }
+        }
+    }
+    if (a.gate_out)
+        for (int h = threadIdx.x; h < H; h += blockDim.x)
+            a.gate_out[(size_t)t * H + h] = 1.0f / (1.0f + expf(-pr[a.g_off + h]));
+}
+
+// ---------------------------------------------------------------- y = g' * sigmoid(alpha g') * (u' + 1), g' = min(g, lim), u' = clamp(u)
+template <typename AT>
+__global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT* __restrict__ out, int64_t ldo, int64_t R, int F,
+                                   float limit, float alpha, const int32_t* __restrict__ n_rows_dev) {
+    const int64_t n = (n_rows_dev ? (int64_t)*n_rows_dev : R) * F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F; const int c = (int)(i % F);
+        const float g = fminf(gu[(size_t)r * ld + c], limit);
+        const float u = fminf(fmaxf(gu[(size_t)r * ld + F + c], -limit), limit);
+        stv(out + (size_t)r * ldo + c, g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    }
+}
+
+// ---------------------------------------------------------------- router: fp32 logits, top-k (ties: lower index), softmax over the chosen
+template <typename AT>
+__global__ void router_topk_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr, const float* __restrict__ br,
+                                   int T, int W, int E, int top, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float z_all[];                         // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = blockIdx.x * nw + warp;
+    if (t >= T) return;
+    float* z = z_all + (size_t)warp * E;
+    const AT* xr = x + (size_t)t * ldx;
+    for (int e = 0; e < E; e++) {
+        float s = 0.f;
+        for (int i = lane; i < W; i += 32) s = fmaf(ldv(xr + i), Wr[(size_t)e * W + i], s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s + br[e];
+    }
+    __syncwarp();
+    if (lane == 0) {
+        float zmax = 0.f, den = 0.f;
+        for (int j = 0; j < top; j++) {
+            int best = -1; float bv = 0.f;
+            for (int e = 0; e < E; e++) {
+                bool taken = false;
+                for (int q = 0; q < j; q++) taken |= ids[(size_t)t * top + q] == e;
+                if (!taken && (best < 0 || z[e] > bv)) { best = e; bv = z[e]; }
+            }
+            ids[(size_t)t * top + j] = best;
+            if (j == 0) zmax = bv;
+            const float w = expf(bv - zmax);
+            wts[(size_t)t * top + j] = w;
+            den += w;
+        }
+        for (int j = 0; j < top; j++) wts[(size_t)t * top + j] /= den;
+    }
+}
+
+// ---------------------------------------------------------------- expert sort: CTA e lists the (token, choice) pairs routed to expert e, in
+// token order, behind those of the experts before it. seg[e] = first sorted row of expert e, seg[E] = n; order[r] = token * top +
+// choice of sorted row r; where[token * top + choice] = r.
+__global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n, int E, int32_t* __restrict__ seg,
+                                int32_t* __restrict__ order, int32_t* __restrict__ where) {
+    __shared__ int sh_w[33];
+    __shared__ int sh_base;
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    int below = 0;
+    for (int i = tid; i < n; i += blockDim.x) below += ids[i] < e;
+    // block total of `below`
+    for (int o = 16; o > 0; o >>= 1) below += __shfl_xor_sync(0xffffffffu, below, o);
+    if (lane == 0) sh_w[warp] = below;
+    __syncthreads();
+    if (tid == 0) { int s = 0; for (int i = 0; i < nw; i++) s += sh_w[i]; sh_base = s; seg[e] = s; }
+    __syncthreads();
+    int base = sh_base;
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+        const int i = i0 + tid;
+        const bool mine = i < n && ids[i] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, mine);
+        const int in_warp = __popc(bal & ((1u << lane) - 1));
+        __syncthreads();
+        if (lane == 0) sh_w[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < nw; w++) { const int c = sh_w[w]; if (w < warp) before += c; total += c; }
+        if (mine) { const int r = base + before + in_warp; order[r] = i; where[i] = r; }
+        base += total;
+    }
+    if (e == E - 1 && tid == 0) seg[E] = n;
+}
+
+// ---------------------------------------------------------------- out[t] = sum_j w[t][j] * y[where[t * top + j]]   (j ascending)
+__global__ void moe_combine_kernel(const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ where,
+                                   const float* __restrict__ wts, int top, float* __restrict__ out, int W) {
+    const int64_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; j++) s = fmaf(wts[t * top + j], y[(size_t)where[t * top + j] * ldy + i], s);
+        out[(size_t)t * W + i] = s;
+    }
+}
+
+// ---------------------------------------------------------------- pen[h][dist] = r1_h * ln(1 + r2_h * dist)
+__global__ void distance_penalty_kernel(const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ pen, int H, int n) {
+    const int h = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        pen[(size_t)h * n + i] = r1[h] * log1pf(r2[h] * (float)i);
+}
+}  // namespace
+
+extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
+                                 cudaStream_t st) {
+    if (T == 0) return 0;
+    if (act_f32) embed_rows_kernel<float><<<(unsigned)T, 128, 0, st>>>((const bf16*)table, ids, x, (float*)x_act, W, vocab);
+    else embed_rows_kernel<bf16><<<(unsigned)T, 128, 0, st>>>((const bf16*)table, ids, x, (bf16*)x_act, W, vocab);
+    P3_CHECK_LAUNCH("embed_rows_f32");
+    return 0;
+}
+
+extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* gain, float* x, void* x_act, int act_f32, int64_t T, int W,
+                                    float eps, cudaStream_t st) {
+    if (T == 0) return 0;
+    const int th = W >= 1024 ? 256 : 128;
+    if (act_f32) postnorm_residual_kernel<float><<<(unsigned)T, th, 0, st>>>(y, ldy, gain, x, (float*)x_act, W, eps);
+    else postnorm_residual_kernel<bf16><<<(unsigned)T, th, 0, st>>>(y, ldy, gain, x, (bf16*)x_act, W, eps);
+    P3_CHECK_LAUNCH("postnorm_residual");
+    return 0;
+}
+
+extern "C" int p3_rmsnorm_rows_f32(const float* x, const int32_t* rows, const float* gain, void* out, int out_f32, int64_t R, int W,
+                                   float eps, cudaStream_t st) {
+    if (R == 0) return 0;
+    const int th = W >= 1024 ? 256 : 128;
+    if (out_f32) rmsnorm_rows_kernel<float><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (float*)out, W, eps);
+    else rmsnorm_rows_kernel<bf16><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (bf16*)out, W, eps);
+    P3_CHECK_LAUNCH("rmsnorm_rows_f32");
+    return 0;
+}
+
+extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
+    P3_CHECK_ARG(a && a->proj && a->q_out && a->k_pool && a->v_pool && a->block_table && a->tok_slot && a->tok_pos, "qkv_post: null argument");
+    P3_CHECK_ARG(a->v_mode == 0 || a->v_first, "qkv_post: value mixing needs the v_first buffer");
+    if (a->T == 0) return 0;
+    const int jobs = a->n_heads + 2 * a->n_kv;
+    const int th = jobs >= 8 ? 256 : 128;
+    if (a->act_f32 && a->cache_f32) qk_norm_kv_write_kernel<float, float><<<a->T, th, 0, st>>>(*a);
+    else if (!a->act_f32 && !a->cache_f32) qk_norm_kv_write_kernel<bf16, bf16><<<a->T, th, 0, st>>>(*a);
+    else P3_CHECK_ARG(false, "qkv_post: activations and cache must both be fp32 or both bf16");
+    P3_CHECK_LAUNCH("qkv_post");
+    return 0;
+}
+
+extern "C" int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, float limit, float alpha,
+                              const int32_t* n_rows_dev, cudaStream_t st) {
+    if (R == 0) return 0;
+    const int64_t n = R * F;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, n_rows_dev);
+    else glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, n_rows_dev);
+    P3_CHECK_LAUNCH("glu_clamped");
+    return 0;
+}
+
+extern "C" int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* br, int T, int W, int E, int top,
+                              int32_t* ids, float* wts, cudaStream_t st) {
+    P3_CHECK_ARG(top >= 1 && top <= E && E <= 1024, "router_topk: need 1 <= top <= experts <= 1024");
+    if (T == 0) return 0;
+    const int nw = 4;
+    const unsigned grid = (unsigned)((T + nw - 1) / nw);
+    const size_t sm = (size_t)nw * E * sizeof(float);
+    if (x_f32) router_topk_kernel<float><<<grid, nw * 32, sm, st>>>((const float*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    else router_topk_kernel<bf16><<<grid, nw * 32, sm, st>>>((const bf16*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    P3_CHECK_LAUNCH("router_topk");
+    return 0;
+}
+
+extern "C" int p3_moe_sort(const int32_t* ids, int n, int E, int32_t* seg, int32_t* order, int32_t* where, cudaStream_t st) {
+    P3_CHECK_ARG(n >= 1 && E >= 1, "moe_sort: empty");
+    moe_sort_kernel<<<E, 1024, 0, st>>>(ids, n, E, seg, order, where);
+    P3_CHECK_LAUNCH("moe_sort");
+    return 0;
+}
+
+extern "C" int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const float* wts, int top, float* out, int64_t T, int W,
+                              cudaStream_t st) {
+    if (T == 0) return 0;
+    moe_combine_kernel<<<(unsigned)T, 128, 0, st>>>(y, ldy, where, wts, top, out, W);
+    P3_CHECK_LAUNCH("moe_combine");
+    return 0;
+}
+
+extern "C" int p3_distance_penalty_table(const float* r1, const float* r2, float* pen, int H, int n, cudaStream_t st) {
+    P3_CHECK_ARG(H >= 1 && n >= 1, "distance_penalty_table: empty");
+    distance_penalty_kernel<<<dim3((unsigned)((n + 255) / 256), (unsigned)H), 256, 0, st>>>(r1, r2, pen, H, n);
+    P3_CHECK_LAUNCH("distance_penalty_table");
+    return 0;
+}

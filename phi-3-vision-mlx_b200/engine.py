@@ -1,0 +1,239 @@
+"""Continuous-batching engine: the step function, the sequence table and the scheduler for models that run a ragged token
+batch against the shared page pool (paged.PagePool).
+
+The Phi-3 drivers (api._generate) serve one rectangular batch per call: all rows start together and the call ends when the last
+row ends. This engine serves a stream of requests instead:
+
+  Engine.step(entries, end)   one model step. `entries` = [(request id, new token ids, indices among them whose logits are
+                              wanted)]; a request is admitted at its first entry, may skip steps, and may bring any number of
+                              tokens (a prompt portion cut anywhere, or one decoded token). All entries run as ONE batch.
+                              `end` = requests whose slot and pages go back to the pool after the step.
+  Scheduler                   greedy / nucleus generation on top of step(): admits waiting prompts while slots and pages last,
+                              cuts long prompts into portions under a token budget per step, runs the portions beside the
+                              single decoded tokens of the running requests, samples on the device with the framework's
+                              p3_row_stats / p3_top_p_sample kernels, and frees a request's pages the step it finishes.
+
+A model plugs in with kv_layout(), cache_dtype(), prepare(max_context) and forward(StepBatch, pool) (tagenex.TagenexB200).
+"""
+import numpy as np
+import torch
+from . import _lib
+from ._lib import call, ptr
+from .paged import PagePool, PoolExhausted, PAGE
+from .tagenex import StepBatch
+
+Q_TILE = 32          # query rows per CTA of the prefill attention kernel (csrc/attention_window.cu)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Engine:
+    def __init__(self, model, max_tokens, n_slots=4):
+        self.model, self.dev = model, model.dev
+        self.pool = PagePool(model.kv_layout(), max_tokens, n_slots, model.cache_dtype(), self.dev)
+        model.prepare(self.pool.n_pages * PAGE)
+        self.slot_of = {}                                    # request id -> slot
+        self.steps = 0
+
+    # ------------------------------------------------------------------ sequence table
+    def length(self, rid):
+        return self.pool.length[self.slot_of[rid]]
+
+    def live(self):
+        return list(self.slot_of)
+
+    def finish(self, rid):
+        self.pool.release(self.slot_of.pop(rid))
+
+    def can_take(self, rid, n_new):
+        """would `n_new` more tokens of request `rid` (known or new) fit right now?"""
+        if rid in self.slot_of:
+            return self.pool.can_extend(self.slot_of[rid], n_new)
+        return bool(self.pool.free_slots) and -(-n_new // PAGE) <= len(self.pool.free_pages)
+
+    # ------------------------------------------------------------------ one step
+    def build_batch(self, entries):
+        """host side of a step: slots, pages, positions, attention tiles -> one int32 upload"""
+        pool = self.pool
+        ids, slots, poss, pf, dec, want = [], [], [], [], [], []
+        row = 0
+        for rid, toks, wanted in entries:
+            n = len(toks)
+            if n == 0:
+                continue
+            if rid not in self.slot_of:
+                self.slot_of[rid] = pool.admit()
+            s = self.slot_of[rid]
+            p0 = pool.extend(s, n)
+            ids.extend(int(t) for t in toks)
+            slots.extend([s] * n)
+            poss.extend(range(p0, p0 + n))
+            if n == 1:
+                dec.append((row, 1, s, p0))
+            else:
+                for r0 in range(0, n, Q_TILE):
+                    pf.append((row + r0, min(Q_TILE, n - r0), s, p0 + r0))
+            for i in wanted:
+                if not 0 <= i < n:
+                    raise IndexError(f'request {rid}: wanted index {i} outside its {n} tokens')
+                want.append(row + i)
+            row += n
+        T = row
+        b = StepBatch()
+        b.T, b.n_pf, b.n_dec, b.R = T, len(pf), len(dec), len(want)
+        b.max_pos = max(poss) if poss else 0
+        if T == 0:
+            return b
+        flat = np.concatenate([np.asarray(ids, np.int32), np.asarray(slots, np.int32), np.asarray(poss, np.int32),
+                               np.asarray(pf, np.int32).reshape(-1), np.asarray(dec, np.int32).reshape(-1),
+                               np.asarray(want, np.int32)])
+        pad = (-3 * T) % 4                                   # tile records are read as 16-byte vectors
+        flat = np.concatenate([flat[:3 * T], np.zeros(pad, np.int32), flat[3 * T:]])
+        d = torch.from_numpy(flat).to(self.dev)
+        b.ids, b.tok_slot, b.tok_pos = d[:T], d[T:2 * T], d[2 * T:3 * T]
+        o = 3 * T + pad
+        b.pf_tiles = d[o:o + 4 * b.n_pf]
+        o += 4 * b.n_pf
+        b.dec_tiles = d[o:o + 4 * b.n_dec]
+        o += 4 * b.n_dec
+        b.want_rows = d[o:o + b.R]
+        pool.sync()
+        return b
+
+    def step(self, entries, end=(), trace=None):
+        """-> fp32 logits [number of wanted rows, vocab] on the device (None if nothing is wanted), rows in the order of the
+        entries and of their wanted indices"""
+        b = self.build_batch(entries)
+        logits = self.model.forward(b, self.pool, trace=trace) if b.T else None
+        for rid in end:
+            if rid in self.slot_of:
+                self.finish(rid)
+        self.steps += 1
+        return logits
+
+
+class _Seq:
+    __slots__ = ('rid', 'prompt', 'fed', 'out', 'max_new', 'done')
+
+    def __init__(self, rid, prompt, max_new):
+        self.rid, self.prompt, self.fed, self.out, self.max_new, self.done = rid, list(prompt), 0, [], max_new, False
+
+
+class Scheduler:
+    """Generation over Engine.step with continuous batching and chunked prefill.
+
+    token_budget   most tokens one step may run (decoded tokens first, the rest goes to prompt portions)
+    chunk          longest prompt portion of one request in one step
+    Sampling is greedy (top_p None) or nucleus; both run on the device, one host read of the sampled ids per step."""
+
+    def __init__(self, engine, token_budget=2048, chunk=512, eos_id=None, top_p=None, temperature=1.0, seed=0):
+        self.e, self.budget, self.chunk, self.eos = engine, int(token_budget), int(chunk), eos_id
+        self.top_p, self.temperature = top_p, float(temperature)
+        self.gen = torch.Generator(device=engine.dev).manual_seed(int(seed))
+        self.waiting, self.running = [], []
+        self._next = 0
+
+    def add(self, prompt, max_new):
+        if len(prompt) == 0:
+            raise ValueError('empty prompt')
+        if -(-(len(prompt) + max_new) // PAGE) > self.e.pool.n_pages:
+            raise PoolExhausted(f'a request of {len(prompt)} + {max_new} tokens can never fit the page pool')
+        s = _Seq(self._next, prompt, int(max_new))
+        self._next += 1
+        self.waiting.append(s)
+        return s
+
+    def _sample(self, logits):
+        R, V = logits.shape
+        tok = torch.empty(R, dtype=torch.int32, device=logits.device)
+        if self.top_p is None:
+            call('p3_row_stats', ptr(logits), R, logits.stride(0), V, ptr(tok), None, None, 0, None, None, 0, None, None, _stream())
+        else:
+            u = torch.rand(R, generator=self.gen, device=logits.device)
+            call('p3_top_p_sample', ptr(logits), R, logits.stride(0), V, float(self.top_p), self.temperature, ptr(u), ptr(tok),
+                 None, None, 0, _stream())
+        return tok.tolist()
+
+    def step(self):
+        """plan one batch, run it, sample; returns the sequences that finished in this step"""
+        e = self.e
+        entries, samplers, budget = [], [], self.budget
+        reserved = 0                                          # pages promised to earlier entries of this step
+        free = len(e.pool.free_pages)
+
+        def pages_for(s, n):
+            return e.pool.pages_needed(e.slot_of[s.rid], n) if s.rid in e.slot_of else -(-n // PAGE)
+
+        for s in self.running:                                # running requests first: one decoded token or the next portion
+            if budget <= 0:
+                break
+            if s.fed < len(s.prompt):
+                n = min(self.chunk, len(s.prompt) - s.fed, budget)
+                toks = s.prompt[s.fed:s.fed + n]
+            else:
+                n, toks = 1, [s.out[-1]]
+            need = pages_for(s, n)
+            if reserved + need > free:
+                continue                                      # waits for pages that a finishing request will give back
+            reserved += need
+            last = s.fed + n >= len(s.prompt)
+            entries.append((s.rid, toks, [n - 1] if last else []))
+            if last:
+                samplers.append(s)
+            s.fed += n
+            budget -= n
+        while self.waiting and budget > 0 and len(e.slot_of) + sum(1 for x in entries if x[0] not in e.slot_of) < e.pool.n_slots:
+            s = self.waiting[0]
+            n = min(self.chunk, len(s.prompt), budget)
+            # admit only if the whole request can still get its pages (no preemption in this scheduler)
+            total = -(-(len(s.prompt) + s.max_new) // PAGE)
+            held = sum(-(-(len(r.prompt) + r.max_new) // PAGE) for r in self.running)
+            if held + total > e.pool.n_pages:
+                break
+            self.waiting.pop(0)
+            self.running.append(s)
+            reserved += -(-n // PAGE)
+            last = n >= len(s.prompt)
+            entries.append((s.rid, s.prompt[:n], [n - 1] if last else []))
+            if last:
+                samplers.append(s)
+            s.fed = n
+            budget -= n
+        if not entries:
+            if self.running or self.waiting:
+                raise PoolExhausted('no request can make progress: the page pool is too small for the running set')
+            return []
+        logits = e.step(entries)
+        finished = []
+        if samplers:
+            toks = self._sample(logits)
+            for s, t in zip(samplers, toks):
+                s.out.append(int(t))
+                if len(s.out) >= s.max_new or (self.eos is not None and t == self.eos):
+                    s.done = True
+        for s in [s for s in self.running if s.done]:
+            self.running.remove(s)
+            e.finish(s.rid)
+            finished.append(s)
+        return finished
+
+    def run(self):
+        done = []
+        while self.running or self.waiting:
+            done.extend(self.step())
+        return sorted(done, key=lambda s: s.rid)
+
+
+def generate_tokens(model, prompts, max_new=32, max_tokens=None, n_slots=4, eos_id=None, top_p=None, temperature=1.0, seed=0,
+                    token_budget=2048, chunk=512):
+    """prompts: list of token-id lists -> list of generated id lists (greedy unless top_p is given). The pool holds `max_tokens`
+    tokens (default: enough for n_slots of the longest request)."""
+    if max_tokens is None:
+        longest = max(len(p) for p in prompts) + max_new
+        max_tokens = n_slots * (-(-longest // PAGE) * PAGE)
+    sch = Scheduler(Engine(model, max_tokens, n_slots), token_budget, chunk, eos_id, top_p, temperature, seed)
+    seqs = [sch.add(p, max_new) for p in prompts]
+    sch.run()
+    return [s.out for s in seqs]
