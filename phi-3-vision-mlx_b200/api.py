@@ -37,6 +37,7 @@ from .configs import PHI35_MINI, PHI35_VISION, ID_EOS, with_overrides
 from .model import Phi3B200, _stream, capture_graph
 from .processor import Phi3FProcessor, Phi3VProcessor, ByteTokenizer
 from .weights import random_weights
+from . import registry
 
 PATH_ORIGINAL_PHI3_VISION = 'models/phi3_v'             # pv:38-41
 PATH_ORIGINAL_PHI3_BLIND = 'models/phi3_mini_128k'
@@ -146,6 +147,10 @@ def load(blind_model=False, quantize_model=False, quantize_cache=False, use_adap
     weights = kwargs.pop('weights', None)
     clip_cfg = kwargs.pop('clip_cfg', None)
     num_crops = kwargs.pop('num_crops', 16)
+    dtype = kwargs.pop('dtype', None)
+    paged = _load_paged(kwargs.get('model_path') if weights is None else weights, cfg, tokenizer, device, dtype)
+    if paged is not None:
+        return paged
     default_path = PATH_ORIGINAL_PHI3_BLIND if blind_model else PATH_ORIGINAL_PHI3_VISION
     if quantize_model and os.path.isdir(default_path + '_Q') and 'model_path' not in kwargs and weights is None:
         default_path += '_Q'                                               # pv:1306-1315: the pre-quantised checkpoint directory
@@ -192,6 +197,58 @@ def load(blind_model=False, quantize_model=False, quantize_cache=False, use_adap
         blind_model = not cfg.architectures[0].startswith('Phi3V')
     processor = Phi3FProcessor(tokenizer) if blind_model else Phi3VProcessor(tokenizer, num_crops=num_crops, device=device)
     return model, processor
+
+
+def _load_paged(src, cfg, tokenizer, device, dtype):
+    """(model, processor) when the checkpoint's config.json (or the given config dict) names a design that runs on the
+    continuous-batching engine (registry entry with engine == 'paged'), else None. `src`: checkpoint folder or weight dict."""
+    raw = cfg if isinstance(cfg, dict) else None
+    if raw is None and isinstance(src, str) and os.path.exists(os.path.join(src, 'config.json')):
+        raw = registry.read_config(src)
+    if raw is None or registry.arch_of(raw) not in registry.names():
+        return None
+    ent = registry.entry_for(raw)
+    if ent.engine != 'paged':
+        return None
+    if src is None:
+        raise ValueError('a paged-engine model needs weights= (a tensor dict) or model_path= (a checkpoint folder)')
+    weights = registry.read_weights(src) if isinstance(src, str) else src
+    mcfg = ent.config(raw)
+    model = ent.build(mcfg, weights, device=device, dtype=dtype or torch.bfloat16)
+    if tokenizer is None:
+        if isinstance(src, str) and os.path.exists(os.path.join(src, 'tokenizer.json')):
+            tokenizer = _load_tokenizer(src)
+        else:
+            tokenizer = ByteTokenizer(vocab_size=mcfg.vocab_size)
+    return model, Phi3FProcessor(tokenizer)
+
+
+def _is_paged(model):
+    return hasattr(model, 'kv_layout')
+
+
+def _generate_paged(model, processor, prompt, max_tokens=512, verbose=True, return_tps=False, return_tokens=False, top_p=None,
+                    temperature=1.0, seed=0, n_slots=4, pool_tokens=None, eos_id=None):
+    """generate() for models of the continuous-batching engine: prompts (a string, a list of strings, or lists of token ids)
+    become requests of engine.Scheduler; they are admitted as slots and pages allow, prefilled in portions beside the decoding
+    of earlier ones, sampled on the device. Returns text(s), or the generated ids with return_tokens."""
+    from .engine import generate_tokens
+    single = isinstance(prompt, str) or (len(prompt) > 0 and isinstance(prompt[0], int))
+    items = [prompt] if single else list(prompt)
+    ids = [list(p) if not isinstance(p, str) else list(processor.tokenizer(p).input_ids) for p in items]
+    tic = Tic()
+    outs = generate_tokens(model, ids, max_new=max_tokens, max_tokens=pool_tokens, n_slots=n_slots, eos_id=eos_id, top_p=top_p,
+                           temperature=temperature, seed=seed)
+    dt = tic()
+    n_in, n_out = sum(len(p) for p in ids), sum(len(o) for o in outs)
+    if verbose:
+        print(f"\nGenerate: {n_out / dt:.2f} tokens-per-sec ({n_in} prompt + {n_out} new tokens / {dt:.1f} sec)")
+    if return_tokens:
+        return outs[0] if single else outs
+    if return_tps:
+        return n_in / dt, n_out / dt
+    texts = [processor.tokenizer.decode(o) for o in outs]
+    return texts[0] if single else texts
 
 
 def _read_adapter(path):
@@ -414,6 +471,10 @@ def _generate(model, processor, prompt, images=None, max_tokens=512, verbose=Tru
     (TokenStopper, pv:106-117) is polled every `eos_check_every` steps instead of twice per token —
     rows are truncated at their first EOS afterwards exactly as the reference does (pv:73).
     `dict_input`: a prebuilt model input (generate_batch) instead of processor(prompt, images)."""
+    if _is_paged(model):
+        if images is not None:
+            raise ValueError(f'{type(model).__name__} takes text only')
+        return _generate_paged(model, processor, prompt, max_tokens, verbose, return_tps, return_tokens, top_p, temperature, seed)
     if dict_input is None and images is not None and isinstance(prompt, list):
         raise ValueError('Images cannot be provided when prompt is a list')
     streamer = Streamer(processor, stream, mute)
@@ -495,6 +556,8 @@ def generate(prompt, images=None, preload=None, blind_model=False, quantize_mode
     if preload is None:
         preload = load(blind_model=blind_model, quantize_model=quantize_model, quantize_cache=quantize_cache,
                        use_adapter=use_adapter)
+    if _is_paged(preload[0]):                                              # plain language model: no chat tags in its vocabulary
+        return _generate(*preload, prompt, images, max_tokens, verbose, return_tps)
     prompt, images = _apply_chat_template(prompt, images, verbose, apply_chat_template)
     return _generate(*preload, prompt, images, max_tokens, verbose, return_tps, early_stop, stream)
 
@@ -513,6 +576,8 @@ def generate_batch(prompts, images=None, preload=None, blind_model=False, quanti
         preload = load(blind_model=blind_model, quantize_model=quantize_model, quantize_cache=quantize_cache,
                        use_adapter=use_adapter)
     model, processor = preload
+    if _is_paged(model):
+        return _generate_paged(model, processor, list(prompts), max_tokens, verbose, return_tps, return_tokens)
     texts, imgs = [], []
     for i, p in enumerate(prompts):
         im = None if images is None else images[i]

@@ -57,6 +57,16 @@ class Engine:
     def build_batch(self, entries):
         """host side of a step: slots, pages, positions, attention tiles -> one int32 upload"""
         pool = self.pool
+        # refuse the whole step before anything is taken if its slots or pages cannot be had
+        new_ids = {rid for rid, toks, _ in entries if len(toks) and rid not in self.slot_of}
+        if len(new_ids) > len(pool.free_slots):
+            raise PoolExhausted(f'{len(new_ids)} new requests but {len(pool.free_slots)} of {pool.n_slots} sequence slots free')
+        grow = {}
+        for rid, toks, _ in entries:
+            grow[rid] = grow.get(rid, 0) + len(toks)
+        need = sum(pool.pages_needed(self.slot_of[r], n) if r in self.slot_of else -(-n // PAGE) for r, n in grow.items())
+        if need > len(pool.free_pages):
+            raise PoolExhausted(f'page pool exhausted: the step wants {need} pages, {len(pool.free_pages)} of {pool.n_pages} free')
         ids, slots, poss, pf, dec, want = [], [], [], [], [], []
         row = 0
         for rid, toks, wanted in entries:

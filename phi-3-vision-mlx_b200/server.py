@@ -174,7 +174,8 @@ def serve(generate_fn, port=8000, max_batch=16, window_ms=2.0, host='', group_ke
 def run(port=8000, max_batch=16, window_ms=2.0, **load_kwargs):
     from . import api
     preload = api.load(**load_kwargs)                        # srv:5: the model is loaded once, at start-up
-    httpd = serve(model_generate_fn(preload), port, max_batch, window_ms, group_key=rope_side_key(preload))
+    paged = hasattr(preload[0], 'kv_layout')              # engine models: no LongRoPE switch to group by
+    httpd = serve(model_generate_fn(preload), port, max_batch, window_ms, group_key=None if paged else rope_side_key(preload))
     print(f'Starting server on port {port}')
     try:
         httpd.serve_forever()
@@ -187,7 +188,9 @@ if __name__ == '__main__':
     ap.add_argument('--port', type=int, default=8000)
     ap.add_argument('--max-batch', type=int, default=16)
     ap.add_argument('--window-ms', type=float, default=2.0)
+    ap.add_argument('--model-path', default=None, help='checkpoint folder; its config.json picks the model class')
     ap.add_argument('--quantize-model', action='store_true')
     ap.add_argument('--quantize-cache', action='store_true')
     a = ap.parse_args()
-    run(a.port, a.max_batch, a.window_ms, quantize_model=a.quantize_model, quantize_cache=a.quantize_cache)
+    extra = {'model_path': a.model_path} if a.model_path else {}
+    run(a.port, a.max_batch, a.window_ms, quantize_model=a.quantize_model, quantize_cache=a.quantize_cache, **extra)

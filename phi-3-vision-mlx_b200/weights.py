@@ -93,3 +93,65 @@ def random_weights(cfg, seed=0, device='cpu', clip_cfg=None, vision=None, init='
         emb = w['model.embed_tokens.weight'].to(torch.float32)
         w['lm_head.weight'] = (PEAK_ALPHA * emb[perm.to(emb.device)]).to(torch.bfloat16)
     return w
+
+
+def tagenex_tensor_shapes(cfg):
+    """name -> shape of every tensor of a Tagenex checkpoint; cfg = the config.json dict"""
+    W, V = cfg['width'], cfg['vocab']
+    out = {'embed': (V, W)}
+    for i, lc in enumerate(cfg['layers']):
+        p, m = f'l{i}.', lc['mixer']
+        H, G, d = m['heads'], m.get('kv_heads', m['heads']), m['dim']
+        dv = m.get('vdim', d)
+        out.update({p + 'norm1': (W,), p + 'mix.q': (H * d, W), p + 'mix.k': (G * d, W), p + 'mix.v': (G * dv, W),
+                    p + 'mix.q.norm': (d,), p + 'mix.k.norm': (d,), p + 'mix.vmix': (), p + 'mix.r1': (H,), p + 'mix.r2': (H,),
+                    p + 'mix.sink': (H,), p + 'mix.g': (H, W), p + 'mix.o': (W, H * dv)})
+        f = lc.get('mlp')
+        if f is None:
+            continue
+        out[p + 'norm2'] = (W,)
+        if f['kind'] == 'dense':
+            F = f['ff']
+            out.update({p + 'mlp.gate': (F, W), p + 'mlp.gate.b': (F,), p + 'mlp.up': (F, W), p + 'mlp.up.b': (F,),
+                        p + 'mlp.down': (W, F), p + 'mlp.down.b': (W,)})
+        else:
+            F, E = f['expert']['ff'], f['router']['experts']
+            for e in range(E):
+                out.update({f'{p}mlp.e{e}.gate': (F, W), f'{p}mlp.e{e}.up': (F, W), f'{p}mlp.e{e}.down': (W, F)})
+            out.update({p + 'mlp.router': (E, W), p + 'mlp.router.b': (E,)})
+    out.update({'final.norm': (W,), 'head': (V, W)})
+    return out
+
+
+def random_tagenex_weights(cfg, seed=0, device='cpu'):
+    """Seeded bf16 tensors for a Tagenex config dict: matrices N(0, 1/fan_in), embedding N(0,1), norm gains 1 + 0.1 N (sublayer
+    norms 0.5 + 0.1 N so the residual grows slowly), biases 0.3 N, router logits of unit spread, penalties r1 in [0.2, 1.2],
+    r2 in [0.05, 1], sinks N(0,1), mixing weight in [0.2, 0.8]."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda s: torch.randn(s, generator=g, device=device, dtype=torch.float32)
+    ru = lambda s, lo, hi: torch.rand(s, generator=g, device=device, dtype=torch.float32) * (hi - lo) + lo
+    w = {}
+    for name, shape in tagenex_tensor_shapes(cfg).items():
+        leaf = name.split('.', 1)[1] if name.startswith('l') and '.' in name else name
+        if name == 'embed':
+            t = rn(shape)
+        elif leaf in ('norm1', 'norm2'):
+            t = 0.5 + 0.1 * rn(shape)
+        elif leaf.endswith('norm'):
+            t = 1.0 + 0.1 * rn(shape)
+        elif leaf == 'mix.vmix':
+            t = ru(shape, 0.2, 0.8)
+        elif leaf == 'mix.r1':
+            t = ru(shape, 0.2, 1.2)
+        elif leaf == 'mix.r2':
+            t = ru(shape, 0.05, 1.0)
+        elif leaf == 'mix.sink':
+            t = rn(shape)
+        elif leaf.endswith('.b'):
+            t = 0.3 * rn(shape)
+        elif leaf == 'mlp.router':
+            t = rn(shape) * (3.0 / shape[1] ** 0.5)
+        else:
+            t = rn(shape) / shape[-1] ** 0.5
+        w[name] = t.to(torch.bfloat16)
+    return w
