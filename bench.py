@@ -472,6 +472,134 @@ def _emit(line):
         os.write(_RESULT_FD, data)
 
 
+# ------------------------------------------------------------------------------------------------ --arch tagenex
+def _tagenex_cfg(width, heads, kv, dim, ff, layers, window, vocab, moe):
+    att = {'type': 'attention', 'mixer': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
+                                          'v_mix': True, 'mask': {'size': window}}}
+    dense = {'kind': 'dense', 'ff': ff, 'limit': 7.0}
+    mix = {'kind': 'moe', 'expert': {'ff': ff // 4, 'limit': 7.0}, 'router': {'experts': 8, 'top': 2}}
+    return {'architecture': 'Tagenex', 'vocab': vocab, 'width': width, 'norm': {'eps': 1e-5},
+            'layers': [dict(att, mlp=(mix if (moe and i % 2) else dense)) for i in range(layers)]}
+
+
+def run_tagenex(args):
+    """Throughput of the Tagenex design on the continuous-batching engine at layer sizes of a real model (random weights, bf16
+    serving mode), beside Phi-3 (the closest existing model: same width, heads, feed-forward size and depth) on its own path.
+    One JSON line: per size prefill tok/s and decode tok/s of both, and for Tagenex the time of every kernel family with its
+    achieved FLOP/s or bytes/s against the measured peaks. Device-timed with CUDA events after warm-up; the weights plus the
+    activations of a step exceed L2 at the large sizes."""
+    import torch
+    import phi3_b200  # noqa: F401
+    from phi3_b200 import configs, weights
+    from phi3_b200.engine import Engine
+    from phi3_b200.tagenex import TagenexB200
+    from phi3_b200.model import Phi3B200
+    hbm, _ = peaks()
+    tf = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))).get('bf16_tflops', 1590.0) if os.path.exists(
+        os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 1590.0
+    dev = torch.device('cuda:0')
+    sizes = [dict(name='w3072_h32x96_ff8192_L4', width=3072, heads=32, kv=32, dim=96, ff=8192, layers=4, window=1024, moe=False),
+             dict(name='w3072_h32x96_kv8_moe_L4', width=3072, heads=32, kv=8, dim=96, ff=8192, layers=4, window=1024, moe=True),
+             dict(name='w1024_h8x128_kv2_moe_L4', width=1024, heads=8, kv=2, dim=128, ff=4096, layers=4, window=512, moe=True)]
+    vocab, B, L, CTX_D, NEW_D = 32064, 4, 2048, 2048, 32
+
+    def timed(fn, n):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    out = []
+    for sz in sizes:
+        cfg = _tagenex_cfg(sz['width'], sz['heads'], sz['kv'], sz['dim'], sz['ff'], sz['layers'], sz['window'], vocab, sz['moe'])
+        m = TagenexB200(cfg, weights.random_tagenex_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, vocab, (L,), generator=g).tolist() for _ in range(B)]
+        eng = Engine(m, B * (CTX_D + 64), B)
+
+        def prefill():
+            eng.step([(i, prompts[i], [L - 1]) for i in range(B)], list(range(B)))
+        ms_pf = timed(prefill, args.steps)
+        m.profile = []
+        prefill()
+        torch.cuda.synchronize()
+        fam = {}
+        for kind, a, b, fl, by in m.profile:
+            f = fam.setdefault(kind, [0.0, 0, 0, 0])
+            f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
+        m.profile = None
+        kern_pf = {k: dict(ms=round(v[0], 3), launches=v[3], tflops=round(v[1] / v[0] / 1e9, 1),
+                           frac_of_measured_bf16=round(v[1] / v[0] / 1e9 / tf, 3)) for k, v in fam.items()}
+        # decode: B sequences at CTX_D tokens of context, one token each per step
+        eng.step([(i, prompts[i][:CTX_D - NEW_D - 8], []) for i in range(B)])
+        tok = [1] * B
+
+        def decode():
+            eng.step([(i, [tok[i]], [0]) for i in range(B)])
+        for _ in range(3):
+            decode()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(NEW_D):
+            decode()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_dec = e0.elapsed_time(e1) / NEW_D
+        m.profile = []
+        decode()
+        torch.cuda.synchronize()
+        fam = {}
+        for kind, a, b, fl, by in m.profile:
+            f = fam.setdefault(kind, [0.0, 0, 0, 0])
+            f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
+        m.profile = None
+        kern_dec = {k: dict(ms=round(v[0], 3), launches=v[3], gbs=round(v[2] / v[0] / 1e6, 1),
+                            frac_of_measured_hbm=round(v[2] / v[0] / 1e6 / hbm, 3)) for k, v in fam.items()}
+        row = dict(size=sz['name'], batch=B, prompt=L, tagenex=dict(prefill_tok_s=round(B * L / ms_pf * 1e3), prefill_ms=round(ms_pf, 2),
+                   decode_tok_s=round(B / ms_dec * 1e3), decode_ms_per_step=round(ms_dec, 3), prefill_kernels=kern_pf, decode_kernels=kern_dec))
+        del eng, m
+        torch.cuda.empty_cache()
+        if sz['kv'] == sz['heads'] and sz['dim'] == 96 and not sz['moe']:
+            # Phi-3 at equal size: same width, heads, head size, feed-forward and depth (full attention instead of a window)
+            pc = configs.with_overrides(configs.PHI35_MINI, hidden_size=sz['width'], num_attention_heads=sz['heads'],
+                                        num_key_value_heads=sz['kv'], intermediate_size=sz['ff'], num_hidden_layers=sz['layers'],
+                                        vocab_size=vocab)
+            pm = Phi3B200(pc, weights.random_weights(pc, seed=0, device=dev))
+            ids = torch.tensor(prompts)
+
+            def p_prefill():
+                lg, c = pm(ids, max_tokens=NEW_D + 8, logits_rows='last')
+                c.release()
+            ms_ppf = timed(p_prefill, args.steps)
+            lg, cache = pm(ids[:, :CTX_D - NEW_D - 8], max_tokens=NEW_D + 16, logits_rows='last')
+            ses = pm.decode_session(lg[:, -1].argmax(-1), cache, NEW_D + 8)
+            for _ in range(3):
+                ses.step()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(NEW_D):
+                ses.step()
+            e1.record()
+            torch.cuda.synchronize()
+            row['phi3_equal_size'] = dict(prefill_tok_s=round(B * L / ms_ppf * 1e3), prefill_ms=round(ms_ppf, 2),
+                                          decode_tok_s=round(B / (e0.elapsed_time(e1) / NEW_D) * 1e3),
+                                          decode_ms_per_step=round(e0.elapsed_time(e1) / NEW_D, 3), note='CUDA-graph decode loop')
+            ses.finish()
+            cache.release()
+            del pm
+            torch.cuda.empty_cache()
+        out.append(row)
+    _emit({"metric": "tagenex_prefill_decode_tok_per_s", 'arch': 'tagenex', 'dtype': 'bf16', 'data': 'synthetic', 'n_gpus': 1,
+          'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -479,11 +607,15 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex'],
+                    help='phi3: the headline workload (default); tagenex: prefill / decode throughput of the Tagenex design')
     args = ap.parse_args()
     if not (args.gpus > 1 and int(os.environ.get('WORLD_SIZE', 1)) == 1):      # the self-launching parent just relays its child
         _claim_stdout()
     if args.impl == 'reference':
         return run_reference(args)
+    if args.arch == 'tagenex':
+        return run_tagenex(args)
     world = int(os.environ.get('WORLD_SIZE', 1))
     if args.gpus > 1 and world == 1:
         # convenience: self-launch under torchrun when called directly with --gpus N

@@ -84,6 +84,16 @@ class TagenexB200:
                     L['router'], L['router_b'] = f32(w[q + 'router']), f32(w[q + 'router.b'])
             self.layers.append(L)
         self._pen_len = 0
+        self.profile = None      # bench.py: list of (kind, ev0, ev1, flops, bytes) when instrumenting
+
+    def _ev(self, start=None, kind=None, flops=0, nbytes=0):
+        if self.profile is None:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        if start is not None:
+            self.profile.append((kind, start, e, flops, nbytes))
+        return e
 
     # ------------------------------------------------------------------ what the engine asks of a model
     def kv_layout(self):
@@ -109,6 +119,15 @@ class TagenexB200:
     # ------------------------------------------------------------------ matrix products
     def linear(self, x, w, out, bias32=None, bias16=None):
         """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T + bias"""
+        M, K = x.shape
+        N = w.shape[0]
+        ev = self._ev()
+        try:
+            return self._linear(x, w, out, bias32, bias16)
+        finally:
+            self._ev(ev, 'gemm', 2 * M * N * K, w.numel() * w.element_size() + x.numel() * x.element_size() + out.numel() * out.element_size())
+
+    def _linear(self, x, w, out, bias32=None, bias16=None):
         M, K = x.shape
         N = w.shape[0]
         if (self.use_tc and not self.f32 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
@@ -170,12 +189,19 @@ class TagenexB200:
             w.out, w.ld_out = ptr(att), att.stride(0)
             w.n_heads, w.n_kv, w.dim, w.vdim, w.scale, w.window = H, G, d, dv, m.scale, m.window
             w.act_f32, w.cache_f32 = self.f32, self.f32
+            esz = 4 if self.f32 else 2
             if b.n_pf:
                 w.tiles, w.n_tiles = ptr(b.pf_tiles), b.n_pf
+                ev = self._ev()
                 call_struct('p3_attn_window_prefill', w, st)
+                span = min(m.window, b.max_pos + 1) if m.window else (b.max_pos + 1) // 2
+                self._ev(ev, 'attn_prefill', 2 * (T - b.n_dec) * H * span * (d + dv), 0)
             if b.n_dec:
                 w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
+                ev = self._ev()
                 call_struct('p3_attn_window_decode', w, st)
+                span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
+                self._ev(ev, 'attn_decode', 2 * b.n_dec * H * span * (d + dv), b.n_dec * G * span * (d + dv) * esz)
             self.linear(att, L['o'], y)
             call('p3_postnorm_residual', ptr(y), y.stride(0), ptr(L['norm1']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
             f = L['cfg'].ff
@@ -211,10 +237,14 @@ class TagenexB200:
         where = torch.empty(n, dtype=torch.int32, device=dev)
         call('p3_moe_sort', ptr(ids), n, f.experts, ptr(seg), ptr(order), ptr(where), st)
         gu = torch.empty((n, 2 * f.ff), dtype=torch.float32, device=dev)
+        ev = self._ev()
         self.gemm_any(xa, L['gu'], gu, rows=order, row_div=f.top, seg=seg, n_groups=f.experts, M=n)
+        self._ev(ev, 'moe_gemm', 2 * n * 2 * f.ff * self.W, L['gu'].numel() * L['gu'].element_size())
         hid = torch.empty((n, f.ff), dtype=self.dtype, device=dev)
         call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, n, f.ff, f.limit, TagenexConfig.GLU_ALPHA,
              None, st)
         dn = torch.empty((n, self.W), dtype=torch.float32, device=dev)
+        ev = self._ev()
         self.gemm_any(hid, L['down'], dn, seg=seg, n_groups=f.experts, M=n)
+        self._ev(ev, 'moe_gemm', 2 * n * f.ff * self.W, L['down'].numel() * L['down'].element_size())
         call('p3_moe_combine', ptr(dn), dn.stride(0), ptr(where), ptr(wts), f.top, ptr(y), T, self.W, st)
