@@ -370,7 +370,11 @@ typedef struct {
     int32_t n_heads, n_kv, dim, vdim; float scale; int32_t window;
     int32_t act_f32, cache_f32;
     const int32_t* tiles; int32_t n_tiles;
+    int32_t n_splits; float* ws;   /* decode only: key slices per request (<= 1: none) and their workspace, fp32
+                                      [n_tiles][n_heads][n_splits][vdim + 2] */
 } p3_attn_window_args;
+/* query rows per tile that p3_attn_window_prefill takes for these sizes: 64 on its tensor-core path, else 32 */
+int p3_attn_window_tile_rows(const p3_attn_window_args* args);
 int p3_attn_window_prefill(const p3_attn_window_args* args, cudaStream_t st);
 int p3_attn_window_decode(const p3_attn_window_args* args, cudaStream_t st);
 

@@ -73,6 +73,7 @@ _SIGS = {
     'p3_distance_penalty_table': [_p, _p, _p, _i, _i, _p],
 }
 _STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode']
+ATTN_WINDOW_MMA = os.environ.get('P3_ATTN_WINDOW_MMA', '1') != '0'
 
 _lib = None
 launches = 0          # number of p3_* kernel-launching calls issued (bench.py reports it)
@@ -208,4 +209,5 @@ class AttnWindowArgs(C.Structure):
     _fields_ = [('q', _p), ('ld_q', _l), ('k_pool', _p), ('v_pool', _p), ('block_table', _p), ('bt_stride', C.c_int32),
                 ('sink', _p), ('penalty', _p), ('n_penalty', C.c_int32), ('gate', _p), ('out', _p), ('ld_out', _l),
                 ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('scale', C.c_float),
-                ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32)]
+                ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32),
+                ('n_splits', C.c_int32), ('ws', _p)]

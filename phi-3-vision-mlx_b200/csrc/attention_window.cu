@@ -8,11 +8,13 @@
 // needs; the sink is folded in as the INITIAL state of the online softmax (running max = sink, denominator = 1, no value).
 //   attn_window_prefill_kernel: one CTA = 32 consecutive query tokens of one sequence x one head, key tiles = whole pages, only
 //                               the pages that hold a visible key are visited
-//   attn_window_decode_kernel:  one CTA = one single-token request x one K/V head (all of its query heads share the K/V reads),
-//                               warps stride over the visible keys, partial softmax states merged through shared memory
+//   attn_window_prefill_mma_kernel: the same on the tensor cores (bf16 mode, head sizes that tile), 64 query rows per CTA
+//   attn_window_decode_kernel:  one CTA = one single-token request x one K/V head (all of its query heads share the K/V reads)
+//                               x one slice of the visible keys, one key per lane; slices merged by attn_window_merge_kernel
 #include "common.cuh"
 #include "../../include/phi3_b200.h"
 #include <cfloat>
+#include <cstdlib>
 
 namespace {
 template <typename T> __device__ __forceinline__ float ldv(const T* p);
@@ -145,23 +147,175 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// bf16 serving mode, head sizes that tile (dim % 16 == 0, vdim % 8 == 0, both <= 128): the two products run on the tensor cores
+// (mma.sync m16n8k16, fp32 accumulators). One CTA = up to 64 query rows (4 warps x 16) x one head, key tile = one page. Scores,
+// mask, penalty (staged per tile in shared memory, index row - col + 63), sink and the online softmax stay fp32 in registers; the
+// weights are rounded to bf16 only as the A operand of P.V, taken straight from the score accumulators; V is read with
+// ldmatrix.trans from its row-major page.
+template <int DK, int DN>
+__global__ void __launch_bounds__(128) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8;
+    bf16* Ks = reinterpret_cast<bf16*>(smraw);               // [64][ldk]
+    bf16* Vs = Ks + P3_PAGE * ldk;                           // [64][ldv]
+    float* pen_s = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);   // [128]
+    const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
+    const int row0 = tile.x, nq = tile.y, slot = tile.z, pos0 = tile.w;
+    const int h = blockIdx.y, g = h / (a.n_heads / a.n_kv);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+    const int r0 = warp * 16 + gid, r1 = r0 + 8;             // this thread's two rows of the tile
+    const bf16* q = (const bf16*)a.q + (size_t)h * d;
+    uint32_t qf[DK][4];
+#pragma unroll
+    for (int t = 0; t < DK; t++) {
+        qf[t][0] = qf[t][1] = qf[t][2] = qf[t][3] = 0u;
+        if (t * 16 < d) {
+            const int c = t * 16 + tig * 2;
+            if (r0 < nq) { const bf16* p = q + (size_t)(row0 + r0) * a.ld_q + c; qf[t][0] = *reinterpret_cast<const uint32_t*>(p); qf[t][2] = *reinterpret_cast<const uint32_t*>(p + 8); }
+            if (r1 < nq) { const bf16* p = q + (size_t)(row0 + r1) * a.ld_q + c; qf[t][1] = *reinterpret_cast<const uint32_t*>(p); qf[t][3] = *reinterpret_cast<const uint32_t*>(p + 8); }
+        }
+    }
+    const float sink = a.sink ? a.sink[h] : -FLT_MAX;
+    float m0 = sink, m1 = sink, l0 = (a.sink && tig == 0) ? 1.f : 0.f, l1 = l0;   // row sums are per-thread partials of a quad
+    float o[DN][4];
+#pragma unroll
+    for (int n = 0; n < DN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    const int last = pos0 + nq - 1;
+    const int first = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
+    const float* pen = a.penalty ? a.penalty + (size_t)h * a.n_penalty : nullptr;
+    const int kc = d / 8, vc = dv / 8;                       // 16-byte chunks per row
+    for (int pg = first / P3_PAGE; pg <= last / P3_PAGE; pg++) {
+        const int page = bt[pg];
+        const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
+        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
+        __syncthreads();
+        for (int i = tid; i < P3_PAGE * kc; i += 128)
+            *reinterpret_cast<uint4*>(Ks + (i / kc) * ldk + (i % kc) * 8) = __ldg(reinterpret_cast<const uint4*>(kp) + i);
+        for (int i = tid; i < P3_PAGE * vc; i += 128)
+            *reinterpret_cast<uint4*>(Vs + (i / vc) * ldv + (i % vc) * 8) = __ldg(reinterpret_cast<const uint4*>(vp) + i);
+        {   // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63)
+            const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
+            pen_s[tid] = (pen && dist >= 0) ? pen[min(dist, a.n_penalty - 1)] : 0.f;
+        }
+        __syncthreads();
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+        for (int t = 0; t < DK; t++) {
+            if (t * 16 < d) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const bf16* kr = Ks + (j * 8 + gid) * ldk + t * 16 + tig * 2;
+                    mma_bf16_16816(s[j], qf[t], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+                }
+            }
+        }
+        float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
+                const int dist = pos0 + row - (pg * P3_PAGE + col);
+                const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
+                const float v = vis ? s[j][e] * a.scale - pen_s[row - col + 63] : -FLT_MAX;
+                s[j][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1);
+        m0 = n0; m1 = n1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float v = s[j][e];
+                const float p = v > -FLT_MAX ? __expf(v - ((e < 2) ? n0 : n1)) : 0.f;
+                s[j][e] = p;
+                if (e < 2) ps0 += p; else ps1 += p;
+            }
+        l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+#pragma unroll
+        for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+        for (int t = 0; t < 4; t++) {                        // 16 keys per step
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * t][0], s[2 * t][1]); pa[1] = pack_bf16(s[2 * t][2], s[2 * t][3]);
+            pa[2] = pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]); pa[3] = pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3]);
+            const bf16* vrow = Vs + (t * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + 8 * (lane >> 4);
+#pragma unroll
+            for (int n = 0; n < DN; n += 2) {
+                if (n * 8 < dv) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vrow + n * 8));
+                    mma_bf16_16816(o[n], pa, b0, b1);
+                    if (n + 1 < DN) mma_bf16_16816(o[n + 1], pa, b2, b3);
+                }
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    bf16* out = (bf16*)a.out + (size_t)h * dv;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int row = half ? r1 : r0;
+        if (row >= nq) continue;
+        const float l = half ? l1 : l0;
+        const float gate = a.gate ? a.gate[(size_t)(row0 + row) * a.n_heads + h] : 1.f;
+        const float inv = l > 0.f ? gate / l : 0.f;
+#pragma unroll
+        for (int n = 0; n < DN; n++) {
+            const int c = n * 8 + tig * 2;
+            if (c < dv)
+                *reinterpret_cast<uint32_t*>(out + (size_t)(row0 + row) * a.ld_out + c) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+        }
+    }
+}
+
 constexpr int DW = 4, RMAX = 8;                              // decode: warps per CTA, query heads per pass
 
-template <typename AT, typename CT, int DC, int DVC>
+template <typename CT> __device__ __forceinline__ void load8(const CT* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), e = unpack_bf16(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = e.x; f[7] = e.y;
+}
+
+// Decode: one CTA = one single-token request x one K/V head x one slice of the visible keys (grid.z = n_splits). A warp takes
+// 32 keys at a time, ONE KEY PER LANE: the lane reads its key row in 16-byte pieces and forms the dot products with all query
+// heads of the group (q broadcast from shared memory), so a score costs no cross-lane traffic; the softmax statistics take one
+// warp reduction per 32 keys and head. For P.V the lanes switch to value columns and the weights travel by shuffle. Warps are
+// merged through shared memory; with several slices the CTA writes its unnormalised (max, sum, vector) to the workspace and
+// attn_window_merge_kernel combines them. The sink enters once, as the initial state of slice 0's first warp.
+template <typename AT, typename CT, int DVC>
 __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_window_args a) {
     extern __shared__ __align__(16) float sm[];
-    const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv;
+    const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv, G = a.n_kv;
     float* Qs = sm;                                          // [RMAX][d]
     float* Ms = Qs + RMAX * d;                               // [DW][RMAX]
     float* Ls = Ms + DW * RMAX;                              // [DW][RMAX]
     float* As = Ls + DW * RMAX;                              // [DW][RMAX][dv]
     const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
     const int row = tile.x, slot = tile.z, pos = tile.w;
-    const int g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int per = (((pos - first + 1) + n_splits - 1) / n_splits + 31) & ~31;
+    const int k_lo = first + split * per, k_hi = min(pos + 1, k_lo + per);
     const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
     const AT* q = (const AT*)a.q + (size_t)row * a.ld_q;
-    AT* out = (AT*)a.out + (size_t)row * a.ld_out;
+    const bool vec = (d % 8 == 0) && (((uintptr_t)a.k_pool & 15) == 0);
     for (int h0 = 0; h0 < rep; h0 += RMAX) {
         const int nr = min(RMAX, rep - h0), hb = g * rep + h0;
         __syncthreads();
@@ -170,41 +324,76 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
         float m[RMAX], l[RMAX], acc[RMAX][DVC];
 #pragma unroll
         for (int r = 0; r < RMAX; r++) {
-            const bool s0 = warp == 0 && a.sink && r < nr;   // the sink enters once: as warp 0's initial state
-            m[r] = s0 ? a.sink[hb + r] : -FLT_MAX; l[r] = s0 ? 1.f : 0.f;
+            const bool s0 = split == 0 && warp == 0 && a.sink && r < nr;
+            m[r] = s0 ? a.sink[hb + r] : -FLT_MAX; l[r] = (s0 && lane == 0) ? 1.f : 0.f;      // l: per-lane partial sums
 #pragma unroll
             for (int j = 0; j < DVC; j++) acc[r][j] = 0.f;
         }
-        for (int kpos = first + warp; kpos <= pos; kpos += DW) {
-            const int page = bt[kpos / P3_PAGE], off = kpos % P3_PAGE;
-            const CT* kp = (const CT*)a.k_pool + (((size_t)page * a.n_kv + g) * P3_PAGE + off) * d;
-            const CT* vp = (const CT*)a.v_pool + (((size_t)page * a.n_kv + g) * P3_PAGE + off) * dv;
-            float kr[DC], vr[DVC];
+        for (int kb = k_lo + warp * 32; kb < k_hi; kb += DW * 32) {
+            const int kpos = kb + lane;
+            const bool valid = kpos < k_hi;
+            float s[RMAX];
 #pragma unroll
-            for (int j = 0; j < DC; j++) { const int c = lane + 32 * j; kr[j] = c < d ? ldv(kp + c) : 0.f; }
+            for (int r = 0; r < RMAX; r++) s[r] = 0.f;
+            if (valid) {
+                const CT* kp = (const CT*)a.k_pool + (((size_t)bt[kpos / P3_PAGE] * G + g) * P3_PAGE + kpos % P3_PAGE) * d;
+                if (vec) {
+                    for (int i = 0; i < d; i += 8) {
+                        float kf[8];
+                        load8(kp + i, kf);
 #pragma unroll
-            for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[j] = c < dv ? ldv(vp + c) : 0.f; }
+                        for (int r = 0; r < RMAX; r++) {
+                            if (r >= nr) break;
+                            const float4 qa = *reinterpret_cast<const float4*>(Qs + r * d + i), qb = *reinterpret_cast<const float4*>(Qs + r * d + i + 4);
+                            s[r] = fmaf(qa.x, kf[0], s[r]); s[r] = fmaf(qa.y, kf[1], s[r]); s[r] = fmaf(qa.z, kf[2], s[r]); s[r] = fmaf(qa.w, kf[3], s[r]);
+                            s[r] = fmaf(qb.x, kf[4], s[r]); s[r] = fmaf(qb.y, kf[5], s[r]); s[r] = fmaf(qb.z, kf[6], s[r]); s[r] = fmaf(qb.w, kf[7], s[r]);
+                        }
+                    }
+                } else {
+                    for (int i = 0; i < d; i++) {
+                        const float kv = ldv(kp + i);
+#pragma unroll
+                        for (int r = 0; r < RMAX; r++) { if (r >= nr) break; s[r] = fmaf(Qs[r * d + i], kv, s[r]); }
+                    }
+                }
+            }
             const int dist = pos - kpos;
+            float p[RMAX];
 #pragma unroll
             for (int r = 0; r < RMAX; r++) {
-                if (r >= nr) break;
-                float s = 0.f;
-#pragma unroll
-                for (int j = 0; j < DC; j++) { const int c = lane + 32 * j; if (c < d) s = fmaf(Qs[r * d + c], kr[j], s); }
-                s = warp_sum(s);
-                if (a.penalty) s -= a.penalty[(size_t)(hb + r) * a.n_penalty + min(dist, a.n_penalty - 1)];
-                const float mn = fmaxf(m[r], s), corr = expf(m[r] - mn), p = expf(s - mn);
-                l[r] = l[r] * corr + p;
+                p[r] = 0.f;
+                if (r >= nr) continue;
+                float sv = -FLT_MAX;
+                if (valid) sv = s[r] - (a.penalty ? a.penalty[(size_t)(hb + r) * a.n_penalty + min(dist, a.n_penalty - 1)] : 0.f);
+                const float mn = fmaxf(m[r], warp_max(sv)), corr = expf(m[r] - mn);
+                p[r] = valid ? expf(sv - mn) : 0.f;
+                l[r] = l[r] * corr + p[r];
                 m[r] = mn;
 #pragma unroll
-                for (int j = 0; j < DVC; j++) acc[r][j] = fmaf(p, vr[j], acc[r][j] * corr);
+                for (int j = 0; j < DVC; j++) acc[r][j] *= corr;
+            }
+            const int nk = min(32, k_hi - kb);
+            for (int kk = 0; kk < nk; kk++) {
+                const int kp2 = kb + kk;
+                const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * dv;
+                float vr[DVC];
+#pragma unroll
+                for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[j] = c < dv ? ldv(vp + c) : 0.f; }
+#pragma unroll
+                for (int r = 0; r < RMAX; r++) {
+                    if (r >= nr) break;
+                    const float pk = __shfl_sync(0xffffffffu, p[r], kk);
+#pragma unroll
+                    for (int j = 0; j < DVC; j++) acc[r][j] = fmaf(pk, vr[j], acc[r][j]);
+                }
             }
         }
         // merge the warps' partial states
 #pragma unroll
         for (int r = 0; r < RMAX; r++) {
             if (r >= nr) break;
-            if (lane == 0) { Ms[warp * RMAX + r] = m[r]; Ls[warp * RMAX + r] = l[r]; }
+            const float lt = warp_sum(l[r]);
+            if (lane == 0) { Ms[warp * RMAX + r] = m[r]; Ls[warp * RMAX + r] = lt; }
 #pragma unroll
             for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; if (c < dv) As[(size_t)(warp * RMAX + r) * dv + c] = acc[r][j]; }
         }
@@ -219,9 +408,36 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
                 L = fmaf(Ls[w * RMAX + r], f, L);
                 o = fmaf(As[(size_t)(w * RMAX + r) * dv + c], f, o);
             }
-            const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
-            stv(out + (size_t)(hb + r) * dv + c, L > 0.f ? o * gate / L : 0.f);
+            if (n_splits == 1) {
+                const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
+                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * dv + c, L > 0.f ? o * gate / L : 0.f);
+            } else {
+                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (dv + 2);
+                if (c == 0) { w[0] = M; w[1] = L; }
+                w[2 + c] = o;
+            }
         }
+    }
+}
+
+// combine the slices of one (request, head): out = gate * sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M)
+template <typename AT>
+__global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits) {
+    const int t = blockIdx.x / a.n_heads, h = blockIdx.x % a.n_heads, dv = a.vdim;
+    const int row = reinterpret_cast<const int4*>(a.tiles)[t].x;
+    const float* w = a.ws + ((size_t)t * a.n_heads + h) * n_splits * (dv + 2);
+    float M = -FLT_MAX;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, w[(size_t)s * (dv + 2)]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; s++) { const float ls = w[(size_t)s * (dv + 2) + 1]; if (ls > 0.f) L = fmaf(ls, expf(w[(size_t)s * (dv + 2)] - M), L); }
+    const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + h] : 1.f;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float ls = w[(size_t)s * (dv + 2) + 1];
+            if (ls > 0.f) o = fmaf(w[(size_t)s * (dv + 2) + 2 + c], expf(w[(size_t)s * (dv + 2)] - M), o);
+        }
+        stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / L : 0.f);
     }
 }
 
@@ -260,23 +476,48 @@ int launch_prefill(const p3_attn_window_args* a, cudaStream_t st) {
 template <typename AT, typename CT>
 int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
     const size_t bytes = sizeof(float) * ((size_t)RMAX * a->dim + 2 * DW * RMAX + (size_t)DW * RMAX * a->vdim);
-    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv);
-    const int c = (a->dim + 31) / 32, cv = (a->vdim + 31) / 32;
-#define GO(N, NV)                                                                                          \
-    do { if (set_smem(attn_window_decode_kernel<AT, CT, N, NV>, bytes, "attn_window_decode")) return -1;    \
-         attn_window_decode_kernel<AT, CT, N, NV><<<grid, DW * 32, bytes, st>>>(*a); } while (0)
-#define GOV(N) do { if (cv <= 1) GO(N, 1); else if (cv <= 2) GO(N, 2); else if (cv <= 4) GO(N, 4); else GO(N, 8); } while (0)
-    if (c <= 1) GOV(1); else if (c <= 2) GOV(2); else if (c <= 4) GOV(4); else GOV(8);
-#undef GOV
+    const int ns = a->n_splits > 1 ? a->n_splits : 1;
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
+    const int cv = (a->vdim + 31) / 32;
+#define GO(NV)                                                                                             \
+    do { if (set_smem(attn_window_decode_kernel<AT, CT, NV>, bytes, "attn_window_decode")) return -1;       \
+         attn_window_decode_kernel<AT, CT, NV><<<grid, DW * 32, bytes, st>>>(*a); } while (0)
+    if (cv <= 1) GO(1); else if (cv <= 2) GO(2); else if (cv <= 4) GO(4); else GO(8);
 #undef GO
+    if (ns > 1) attn_window_merge_kernel<AT><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns);
     return 0;
 }
 }  // namespace
 
+static bool prefill_mma_ok(const p3_attn_window_args* a) {
+    static int off = -1;
+    if (off < 0) { const char* e = getenv("P3_ATTN_WINDOW_MMA"); off = (e && e[0] == '0') ? 1 : 0; }
+    return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 128 && a->vdim <= 128 &&
+           a->ld_q % 2 == 0 && a->ld_out % 2 == 0 && ((uintptr_t)a->q & 3) == 0 && ((uintptr_t)a->out & 3) == 0 &&
+           ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0;
+}
+
+static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
+    const size_t bytes = sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + 128 * sizeof(float);
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads);
+    if (a->dim <= 64 && a->vdim <= 64) {
+        if (set_smem(attn_window_prefill_mma_kernel<4, 8>, bytes, "attn_window_prefill")) return -1;
+        attn_window_prefill_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a);
+    } else {
+        if (set_smem(attn_window_prefill_mma_kernel<8, 16>, bytes, "attn_window_prefill")) return -1;
+        attn_window_prefill_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a);
+    }
+    return 0;
+}
+
+/* rows per tile the launch accepts: 64 on the tensor-core path, 32 otherwise */
+extern "C" int p3_attn_window_tile_rows(const p3_attn_window_args* a) { return (a && prefill_mma_ok(a)) ? 64 : BQ; }
+
 extern "C" int p3_attn_window_prefill(const p3_attn_window_args* a, cudaStream_t st) {
     if (check_args(a, "attn_window_prefill")) return -1;
     if (a->n_tiles == 0) return 0;
-    const int rc = a->act_f32 ? launch_prefill<float, float>(a, st) : launch_prefill<bf16, bf16>(a, st);
+    const int rc = prefill_mma_ok(a) ? launch_prefill_mma(a, st)
+                 : a->act_f32 ? launch_prefill<float, float>(a, st) : launch_prefill<bf16, bf16>(a, st);
     if (rc) return rc;
     P3_CHECK_LAUNCH("attn_window_prefill");
     return 0;
@@ -284,6 +525,8 @@ extern "C" int p3_attn_window_prefill(const p3_attn_window_args* a, cudaStream_t
 
 extern "C" int p3_attn_window_decode(const p3_attn_window_args* a, cudaStream_t st) {
     if (check_args(a, "attn_window_decode")) return -1;
+    P3_CHECK_ARG(a->n_splits <= 1 || a->ws, "attn_window_decode: several key slices need the workspace");
+    P3_CHECK_ARG(a->n_splits <= 65535, "attn_window_decode: too many key slices");
     if (a->n_tiles == 0) return 0;
     const int rc = a->act_f32 ? launch_decode<float, float>(a, st) : launch_decode<bf16, bf16>(a, st);
     if (rc) return rc;

@@ -22,7 +22,6 @@ from ._lib import call, ptr
 from .paged import PagePool, PoolExhausted, PAGE
 from .tagenex import StepBatch
 
-Q_TILE = 32          # query rows per CTA of the prefill attention kernel (csrc/attention_window.cu)
 
 
 def _stream():
@@ -34,6 +33,7 @@ class Engine:
         self.model, self.dev = model, model.dev
         self.pool = PagePool(model.kv_layout(), max_tokens, n_slots, model.cache_dtype(), self.dev)
         model.prepare(self.pool.n_pages * PAGE)
+        self.q_tile = int(getattr(model, 'q_tile', 32))      # query rows per CTA of the model's prefill attention kernel
         self.slot_of = {}                                    # request id -> slot
         self.steps = 0
 
@@ -83,8 +83,8 @@ class Engine:
             if n == 1:
                 dec.append((row, 1, s, p0))
             else:
-                for r0 in range(0, n, Q_TILE):
-                    pf.append((row + r0, min(Q_TILE, n - r0), s, p0 + r0))
+                for r0 in range(0, n, self.q_tile):
+                    pf.append((row + r0, min(self.q_tile, n - r0), s, p0 + r0))
             for i in wanted:
                 if not 0 <= i < n:
                     raise IndexError(f'request {rid}: wanted index {i} outside its {n} tokens')

@@ -84,6 +84,11 @@ class TagenexB200:
                     L['router'], L['router_b'] = f32(w[q + 'router']), f32(w[q + 'router.b'])
             self.layers.append(L)
         self._pen_len = 0
+        # query rows per attention tile the engine cuts prompt portions into: 64 when every layer takes the tensor-core prefill
+        # kernel (bf16, key size % 16 == 0, value size % 8 == 0, both <= 128; csrc/attention_window.cu), else 32
+        mma = _lib.ATTN_WINDOW_MMA and not self.f32 and all(
+            l.mixer.dim % 16 == 0 and l.mixer.vdim % 8 == 0 and l.mixer.dim <= 128 and l.mixer.vdim <= 128 for l in cfg.layers)
+        self.q_tile = 64 if mma else 32
         self.profile = None      # bench.py: list of (kind, ev0, ev1, flops, bytes) when instrumenting
 
     def _ev(self, start=None, kind=None, flops=0, nbytes=0):
@@ -198,6 +203,11 @@ class TagenexB200:
                 self._ev(ev, 'attn_prefill', 2 * (T - b.n_dec) * H * span * (d + dv), 0)
             if b.n_dec:
                 w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
+                # slices of the visible keys per request so that two waves of CTAs exist, at least 128 keys per slice
+                span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
+                w.n_splits = max(1, min(-(-2 * 148 // (b.n_dec * G)), -(-span // 128)))
+                ws = e(b.n_dec * H * w.n_splits * (dv + 2)) if w.n_splits > 1 else None
+                w.ws = ptr(ws)
                 ev = self._ev()
                 call_struct('p3_attn_window_decode', w, st)
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1

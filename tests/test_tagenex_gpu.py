@@ -232,7 +232,7 @@ def test_other_sizes(lib, name, width):
 
 
 # ------------------------------------------------------------------------------------------------ mechanisms alone
-def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed=0):
+def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed=0, tile_rows=32, n_splits=1):
     """random q/k/v with a few dominant (query, key) pairs `hot` = [(i, j)]: both rows get a large common component so that
     exp(score) of that pair dwarfs the rest and a wrong mask edge changes the output completely. Returns (kernel out via
     prefill tiles, kernel out via decode tiles, oracle) for all n_ctx queries."""
@@ -280,7 +280,7 @@ def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed
     outs = []
     for kind in ('prefill', 'decode'):
         if kind == 'prefill':
-            tiles = [(r0, min(32, n_ctx - r0), 1, r0) for r0 in range(0, n_ctx, 32)]
+            tiles = [(r0, min(tile_rows, n_ctx - r0), 1, r0) for r0 in range(0, n_ctx, tile_rows)]
         else:
             tiles = [(r, 1, 1, r) for r in range(n_ctx)]
         td = torch.tensor(tiles, dtype=torch.int32, device=dev).reshape(-1)
@@ -291,6 +291,9 @@ def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed
         a_.n_heads, a_.n_kv, a_.dim, a_.vdim, a_.scale, a_.window = H, G, d, dv, scale, window
         a_.act_f32 = a_.cache_f32 = int(dtype == F32)
         a_.tiles, a_.n_tiles = ptr(td), len(tiles)
+        if kind == 'decode' and n_splits > 1:
+            ws = torch.empty(len(tiles) * H * n_splits * (dv + 2), device=dev)
+            a_.n_splits, a_.ws = n_splits, ptr(ws)
         call_struct('p3_attn_window_' + kind, a_, 0)
         torch.cuda.synchronize()
         outs.append(out.float().cpu().reshape(n_ctx, H, dv))
@@ -314,6 +317,23 @@ def test_attention_window_edges_far_keys_and_page_borders(lib, window, dtype):
     tol = 1e-4 if dtype == F32 else 3e-2
     assert (pf.double() - ref).abs().max() < tol
     assert (dc.double() - ref).abs().max() < tol
+
+
+@pytest.mark.parametrize('shape', [(32, 40, 64), (128, 128, 64), (64, 8, 32), (16, 72, 64)])
+@pytest.mark.parametrize('window', [0, 65, 200])
+def test_attention_on_the_tensor_cores_and_with_key_slices(lib, shape, window):
+    """bf16 head sizes that take the mma.sync prefill kernel (64-row tiles), and the decode kernel with 3 and 7 key slices"""
+    d, dv, rows = shape
+    n = 333
+    hot = [(i, i - window + 1) for i in (64, 128, 199, 332) if window and i - window + 1 >= 0]
+    hot += [(i + 1, i + 1 - window) for i in (64, 128, 199, 331) if window and i + 1 - window >= 0]
+    hot += [(i, 0) for i in (63, 64, 332)] if not window else []
+    for splits in (3, 7):
+        pf, dc, ref = _attention_case(lib, B16, H=6, G=2, d=d, dv=dv, window=window, n_ctx=n, hot=hot, scale=d ** -0.5,
+                                      tile_rows=rows, n_splits=splits)
+        assert (pf.double() - ref).abs().max() < 3e-2 and (dc.double() - ref).abs().max() < 3e-2
+    pf, dc, ref = _attention_case(lib, F32, H=6, G=2, d=d, dv=dv, window=window, n_ctx=n, hot=hot, scale=d ** -0.5, n_splits=5)
+    assert (pf.double() - ref).abs().max() < 1e-4 and (dc.double() - ref).abs().max() < 1e-4
 
 
 def test_attention_sink_takes_weight_but_has_no_value(lib):
