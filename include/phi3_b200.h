@@ -335,9 +335,10 @@ int p3_gemm_any(const p3_gemm_any_args* args, cudaStream_t st);
 /* x fp32 [T,W] = table[ids] (bf16 table); x_act (may be NULL) receives the same rows in the activation type */
 int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
                       cudaStream_t st);
-/* norm on a sublayer's OUTPUT: x += y / sqrt(mean(y^2) + eps) * gain; x_act (may be NULL) = the new x in the activation type */
-int p3_postnorm_residual(const float* y, int64_t ldy, const float* gain, float* x, void* x_act, int act_f32, int64_t T, int W,
-                         float eps, cudaStream_t st);
+/* norm on a sublayer's OUTPUT: y' = y + y_bias (y_bias fp32 [W] or NULL: a bias the producing product left out);
+ * x += y' / sqrt(mean(y'^2) + eps) * gain; x_act (may be NULL) = the new x in the activation type */
+int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_bias, const float* gain, float* x, void* x_act, int act_f32,
+                         int64_t T, int W, float eps, cudaStream_t st);
 /* out[r] = rms_norm(x[rows[r]]) * gain (rows NULL: r itself): the model's last norm, only for the rows whose logits are wanted */
 int p3_rmsnorm_rows_f32(const float* x, const int32_t* rows, const float* gain, void* out, int out_f32, int64_t R, int W, float eps,
                         cudaStream_t st);
@@ -378,9 +379,10 @@ int p3_attn_window_tile_rows(const p3_attn_window_args* args);
 int p3_attn_window_prefill(const p3_attn_window_args* args, cudaStream_t st);
 int p3_attn_window_decode(const p3_attn_window_args* args, cudaStream_t st);
 
-/* out (act) [R, F] = g' * sigmoid(alpha g') * (u' + 1), g' = min(gu[:, :F], limit), u' = clamp(gu[:, F:2F], -limit, limit) */
+/* out (act) [R, F] = g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) with
+ * g = gu[:, :F] + bias[:F], u = gu[:, F:2F] + bias[F:] (bias fp32 [2F] or NULL) */
 int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, float limit, float alpha,
-                   const int32_t* n_rows_dev, cudaStream_t st);
+                   const float* bias, cudaStream_t st);
 /* router: z = Wr x + br in fp32; the `top` largest (ties: lower index) -> ids [T, top]; wts = softmax over the chosen logits */
 int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* br, int T, int W, int E, int top, int32_t* ids,
                    float* wts, cudaStream_t st);

@@ -64,7 +64,7 @@ _SIGS = {
     'p3_embed_gather_xg': [_p, _p, _p, _l, _i, _i, _p, _p, _p, _p],
     # decoders with an fp32 residual stream over a shared page pool (csrc/seq_ops.cu)
     'p3_embed_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _i, _p],
-    'p3_postnorm_residual': [_p, _l, _p, _p, _p, _i, _l, _i, _f, _p],
+    'p3_postnorm_residual': [_p, _l, _p, _p, _p, _p, _i, _l, _i, _f, _p],
     'p3_rmsnorm_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _f, _p],
     'p3_glu_clamped': [_p, _l, _p, _l, _i, _l, _i, _f, _f, _p, _p],
     'p3_router_topk': [_p, _l, _i, _p, _p, _i, _i, _i, _i, _p, _p, _p],

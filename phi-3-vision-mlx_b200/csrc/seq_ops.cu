@@ -44,17 +44,17 @@ __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t*
 
 // ---------------------------------------------------------------- x += rms_norm(y) * gain ; activation copy of the new x
 template <typename AT>
-__global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ gain,
-                                         float* __restrict__ x, AT* __restrict__ xa, int W, float eps) {
+__global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ ybias,
+                                         const float* __restrict__ gain, float* __restrict__ x, AT* __restrict__ xa, int W, float eps) {
     __shared__ float sh[32];
     const int64_t t = blockIdx.x;
     const float* yr = y + (size_t)t * ldy;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = yr[i]; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = yr[i] + (ybias ? ybias[i] : 0.f); ss = fmaf(v, v, ss); }
     ss = block_sum(ss, sh);
     const float r = 1.0f / sqrtf(ss / (float)W + eps);
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float v = x[(size_t)t * W + i] + yr[i] * r * gain[i];
+        const float v = x[(size_t)t * W + i] + (yr[i] + (ybias ? ybias[i] : 0.f)) * r * gain[i];
         x[(size_t)t * W + i] = v;
         if (xa) stv(xa + (size_t)t * W + i, v);
     }
@@ -121,12 +121,12 @@ __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
 // ---------------------------------------------------------------- y = g' * sigmoid(alpha g') * (u' + 1), g' = min(g, lim), u' = clamp(u)
 template <typename AT>
 __global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT* __restrict__ out, int64_t ldo, int64_t R, int F,
-                                   float limit, float alpha, const int32_t* __restrict__ n_rows_dev) {
-    const int64_t n = (n_rows_dev ? (int64_t)*n_rows_dev : R) * F;
+                                   float limit, float alpha, const float* __restrict__ bias) {
+    const int64_t n = R * F;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / F; const int c = (int)(i % F);
-        const float g = fminf(gu[(size_t)r * ld + c], limit);
-        const float u = fminf(fmaxf(gu[(size_t)r * ld + F + c], -limit), limit);
+        const float g = fminf(gu[(size_t)r * ld + c] + (bias ? bias[c] : 0.f), limit);
+        const float u = fminf(fmaxf(gu[(size_t)r * ld + F + c] + (bias ? bias[F + c] : 0.f), -limit), limit);
         stv(out + (size_t)r * ldo + c, g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
     }
 }
@@ -228,12 +228,12 @@ extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x
     return 0;
 }
 
-extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* gain, float* x, void* x_act, int act_f32, int64_t T, int W,
-                                    float eps, cudaStream_t st) {
+extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_bias, const float* gain, float* x, void* x_act, int act_f32,
+                                    int64_t T, int W, float eps, cudaStream_t st) {
     if (T == 0) return 0;
     const int th = W >= 1024 ? 256 : 128;
-    if (act_f32) postnorm_residual_kernel<float><<<(unsigned)T, th, 0, st>>>(y, ldy, gain, x, (float*)x_act, W, eps);
-    else postnorm_residual_kernel<bf16><<<(unsigned)T, th, 0, st>>>(y, ldy, gain, x, (bf16*)x_act, W, eps);
+    if (act_f32) postnorm_residual_kernel<float><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (float*)x_act, W, eps);
+    else postnorm_residual_kernel<bf16><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (bf16*)x_act, W, eps);
     P3_CHECK_LAUNCH("postnorm_residual");
     return 0;
 }
@@ -262,12 +262,12 @@ extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
 }
 
 extern "C" int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, float limit, float alpha,
-                              const int32_t* n_rows_dev, cudaStream_t st) {
+                              const float* bias, cudaStream_t st) {
     if (R == 0) return 0;
     const int64_t n = R * F;
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, n_rows_dev);
-    else glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, n_rows_dev);
+    if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
+    else glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
     P3_CHECK_LAUNCH("glu_clamped");
     return 0;
 }

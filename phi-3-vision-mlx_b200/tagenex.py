@@ -52,6 +52,7 @@ class TagenexB200:
         self.f32 = int(dtype == torch.float32)
         self.W, self.V, self.eps = cfg.width, cfg.vocab_size, cfg.eps
         self.use_tc = os.environ.get('P3_LM_TC', '1') != '0'
+        self.use_skinny = os.environ.get('P3_LM_SKINNY', '1') != '0' and hasattr(_lib.lib(), 'p3_gemm_skinny')
         w = weights
         mat = lambda t: t.to(self.dev, dtype).contiguous()                     # matrices: the compute type
         f32 = lambda t: t.to(self.dev, torch.float32).contiguous()            # everything that enters fp32 arithmetic
@@ -123,7 +124,9 @@ class TagenexB200:
 
     # ------------------------------------------------------------------ matrix products
     def linear(self, x, w, out, bias32=None, bias16=None):
-        """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T + bias"""
+        """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T (+ bias). Returns the bias (fp32) that is STILL TO ADD: None
+        when the product added it, bias32 when the kernel has no bias input (the weight-streaming kernel of small batches); the
+        consumer kernel (activation / output norm) then adds it."""
         M, K = x.shape
         N = w.shape[0]
         ev = self._ev()
@@ -135,13 +138,20 @@ class TagenexB200:
     def _linear(self, x, w, out, bias32=None, bias16=None):
         M, K = x.shape
         N = w.shape[0]
-        if (self.use_tc and not self.f32 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-                and w.data_ptr() % 16 == 0 and (bias32 is None or bias16 is not None)):
+        aligned = (not self.f32 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+        if (self.use_skinny and aligned and M <= 16 and K % 64 == 0 and N % 16 == 0 and out.dtype == torch.float32
+                and w.is_contiguous()):
+            # <= 16 tokens: the product is a stream of the weights; the Phi-3 decode kernel does that at HBM speed
+            call('p3_gemm_skinny', ptr(x), x.stride(0), None, self.eps, ptr(w), ptr(out), out.stride(0), None, M, N, K,
+                 _lib.EPI_F32, None, 0, None, None, 0, _stream())
+            return bias32
+        if self.use_tc and aligned and (bias32 is None or bias16 is not None):
             epi = _lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_NONE
             call('p3_gemm', ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias16), ptr(out), out.stride(0), None, None,
                  M, N, K, epi, 0, _stream())
-            return out
-        return self.gemm_any(x, w, out, bias32)
+            return None
+        self.gemm_any(x, w, out, bias32)
+        return None
 
     def gemm_any(self, x, w, out, bias=None, rows=None, row_div=1, seg=None, n_groups=0, M=None):
         a = _lib.GemmAnyArgs()
@@ -203,9 +213,9 @@ class TagenexB200:
                 self._ev(ev, 'attn_prefill', 2 * (T - b.n_dec) * H * span * (d + dv), 0)
             if b.n_dec:
                 w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
-                # slices of the visible keys per request so that two waves of CTAs exist, at least 128 keys per slice
+                # slices of the visible keys per request: enough CTAs for eight per SM, at least 128 keys (one pass of a CTA) per slice
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
-                w.n_splits = max(1, min(-(-2 * 148 // (b.n_dec * G)), -(-span // 128)))
+                w.n_splits = max(1, min(-(-8 * 148 // (b.n_dec * G)), -(-span // 128)))
                 ws = e(b.n_dec * H * w.n_splits * (dv + 2)) if w.n_splits > 1 else None
                 w.ws = ptr(ws)
                 ev = self._ev()
@@ -213,18 +223,20 @@ class TagenexB200:
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
                 self._ev(ev, 'attn_decode', 2 * b.n_dec * H * span * (d + dv), b.n_dec * G * span * (d + dv) * esz)
             self.linear(att, L['o'], y)
-            call('p3_postnorm_residual', ptr(y), y.stride(0), ptr(L['norm1']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
+            call('p3_postnorm_residual', ptr(y), y.stride(0), None, ptr(L['norm1']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
             f = L['cfg'].ff
             if f is not None:
                 if f.kind == 'dense':
                     gu, hid = e(T, 2 * f.ff), e(T, f.ff, dt=act)
-                    self.linear(xa, L['gu'], gu, L['gu_b32'], L['gu_b16'])
+                    left = self.linear(xa, L['gu'], gu, L['gu_b32'], L['gu_b16'])
                     call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, T, f.ff, f.limit,
-                         TagenexConfig.GLU_ALPHA, None, st)
-                    self.linear(hid, L['down'], y, L['down_b32'], L['down_b16'])
+                         TagenexConfig.GLU_ALPHA, ptr(left), st)
+                    left = self.linear(hid, L['down'], y, L['down_b32'], L['down_b16'])
                 else:
                     self._moe(L, f, xa, y, T)
-                call('p3_postnorm_residual', ptr(y), y.stride(0), ptr(L['norm2']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
+                    left = None
+                call('p3_postnorm_residual', ptr(y), y.stride(0), ptr(left), ptr(L['norm2']), ptr(x), ptr(xa), self.f32, T, W,
+                     self.eps, st)
             if trace is not None:
                 trace.append(x.clone())
         if not b.R:

@@ -231,6 +231,28 @@ def test_other_sizes(lib, name, width):
         assert_close(run_schedule(model, toks, [70, 2, 31]), ref, dtype, name)
 
 
+def test_small_batches_take_the_weight_streaming_products(lib):
+    """sizes at which every dense product of a decode step (K % 64 == 0, N % 16 == 0, <= 16 rows) goes to the weight-streaming
+    kernel, biases added by the consumer kernels: decoded logits must equal the prompt path's and the oracle's"""
+    configs, weights, engine, tagenex, paged, O = _mods()
+    layers = [dict(_att(16, 4, 16, 16, 40, True), mlp={'kind': 'dense', 'ff': 192, 'limit': 2.0}),
+              dict(_att(16, 4, 16, 16, 0, True), mlp={'kind': 'moe', 'expert': {'ff': 64, 'limit': 2.0}, 'router': {'experts': 4, 'top': 2}})]
+    cfg = configs.tiny_tagenex(width=128, vocab=208, layers=layers)
+    model, w = make(cfg, B16, seed=15)
+    assert model.use_skinny
+    toks = tokens(100, cfg['vocab'], 16)
+    ref = O.forward(cfg, w, toks, torch.float64)
+    dec = run_schedule(model, toks, [20])                     # 80 single-token steps
+    assert_close(dec, ref, B16)
+    eng = engine.Engine(model, 512, 4)                        # 3 requests decoding together (3 rows per product)
+    eng.step([(i, toks[:60], []) for i in range(3)])
+    together = [eng.step([(i, [toks[60 + s]], [0]) for i in range(3)]) for s in range(40)]
+    for i in range(3):
+        assert_close(torch.stack([t[i] for t in together]), ref[60:], B16)
+    model.use_skinny = False
+    assert_close(run_schedule(model, toks, [20]), dec, B16)
+
+
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed=0, tile_rows=32, n_splits=1):
     """random q/k/v with a few dominant (query, key) pairs `hot` = [(i, j)]: both rows get a large common component so that
