@@ -389,6 +389,8 @@ int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float* Wr, const
 /* stable sort of the n = T * top (token, choice) pairs by expert: seg [E + 1], order [n] (sorted row -> pair), where [n] (pair ->
  * sorted row); feeds p3_gemm_any's segments and p3_moe_combine */
 int p3_moe_sort(const int32_t* ids, int n, int E, int32_t* seg, int32_t* order, int32_t* where, cudaStream_t st);
+/* out[r] = x[rows[r] / div] (activation rows brought into expert order for per-expert dense products) */
+int p3_gather_rows(const void* x, int64_t ldx, int x_f32, const int32_t* rows, int div, void* out, int64_t R, int W, cudaStream_t st);
 int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const float* wts, int top, float* out, int64_t T, int W,
                    cudaStream_t st);
 /* pen[h][i] = r1[h] * ln(1 + r2[h] * i), i < n */

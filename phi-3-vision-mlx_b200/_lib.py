@@ -70,6 +70,7 @@ _SIGS = {
     'p3_router_topk': [_p, _l, _i, _p, _p, _i, _i, _i, _i, _p, _p, _p],
     'p3_moe_sort': [_p, _i, _i, _p, _p, _p, _p],
     'p3_moe_combine': [_p, _l, _p, _p, _i, _p, _l, _i, _p],
+    'p3_gather_rows': [_p, _l, _i, _p, _i, _p, _l, _i, _p],
     'p3_distance_penalty_table': [_p, _p, _p, _i, _i, _p],
 }
 _STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode']

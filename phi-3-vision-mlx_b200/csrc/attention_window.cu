@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
             if (valid) {
                 const CT* kp = (const CT*)a.k_pool + (((size_t)bt[kpos / P3_PAGE] * G + g) * P3_PAGE + kpos % P3_PAGE) * d;
                 if (vec) {
-#pragma unroll 4
+#pragma unroll 8
                     for (int i = 0; i < d; i += 8) {
                         float kf[8];
                         load8(kp + i, kf);
@@ -374,17 +374,18 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
                 for (int j = 0; j < DVC; j++) acc[r][j] *= corr;
             }
             const int nk = min(32, k_hi - kb);
-            for (int k0 = 0; k0 < nk; k0 += 4) {              // four value rows in flight per step
-                float vr[4][DVC];
+            constexpr int VR = DVC <= 2 ? 16 : (DVC <= 4 ? 8 : 4);   // value rows in flight per step
+            for (int k0 = 0; k0 < nk; k0 += VR) {
+                float vr[VR][DVC];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < VR; u++) {
                     const int kp2 = min(kb + k0 + u, k_hi - 1);
                     const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * dv;
 #pragma unroll
                     for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[u][j] = c < dv ? ldv(vp + c) : 0.f; }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < VR; u++) {
 #pragma unroll
                     for (int r = 0; r < RMAX; r++) {
                         if (r >= nr) break;

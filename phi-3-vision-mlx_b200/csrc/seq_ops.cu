@@ -141,11 +141,19 @@ __global__ void router_topk_kernel(const AT* __restrict__ x, int64_t ldx, const 
     if (t >= T) return;
     float* z = z_all + (size_t)warp * E;
     const AT* xr = x + (size_t)t * ldx;
-    for (int e = 0; e < E; e++) {
-        float s = 0.f;
-        for (int i = lane; i < W; i += 32) s = fmaf(ldv(xr + i), Wr[(size_t)e * W + i], s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s + br[e];
+    for (int e0 = 0; e0 < E; e0 += 8) {                      // eight experts per pass over the token's activations
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int i = lane; i < W; i += 32) {
+            const float xv = ldv(xr + i);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (e0 + j < E) s[j] = fmaf(xv, Wr[(size_t)(e0 + j) * W + i], s[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float t = warp_sum(s[j]);
+            if (lane == 0 && e0 + j < E) z[e0 + j] = t + br[e0 + j];
+        }
     }
     __syncwarp();
     if (lane == 0) {
@@ -198,6 +206,15 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n, int E, i
         base += total;
     }
     if (e == E - 1 && tid == 0) seg[E] = n;
+}
+
+// ---------------------------------------------------------------- out[r] = x[rows[r] / div]: rows of the activations in expert order
+template <typename AT>
+__global__ void gather_rows_kernel(const AT* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows, int div,
+                                   AT* __restrict__ out, int W) {
+    const int64_t r = blockIdx.x;
+    const AT* src = x + (size_t)(rows[r] / div) * ldx;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)r * W + i] = src[i];
 }
 
 // ---------------------------------------------------------------- out[t] = sum_j w[t][j] * y[where[t * top + j]]   (j ascending)
@@ -289,6 +306,16 @@ extern "C" int p3_moe_sort(const int32_t* ids, int n, int E, int32_t* seg, int32
     P3_CHECK_ARG(n >= 1 && E >= 1, "moe_sort: empty");
     moe_sort_kernel<<<E, 1024, 0, st>>>(ids, n, E, seg, order, where);
     P3_CHECK_LAUNCH("moe_sort");
+    return 0;
+}
+
+extern "C" int p3_gather_rows(const void* x, int64_t ldx, int x_f32, const int32_t* rows, int div, void* out, int64_t R, int W,
+                              cudaStream_t st) {
+    P3_CHECK_ARG(div >= 1 && rows, "gather_rows: need an index list and div >= 1");
+    if (R == 0) return 0;
+    if (x_f32) gather_rows_kernel<float><<<(unsigned)R, 128, 0, st>>>((const float*)x, ldx, rows, div, (float*)out, W);
+    else gather_rows_kernel<bf16><<<(unsigned)R, 128, 0, st>>>((const bf16*)x, ldx, rows, div, (bf16*)out, W);
+    P3_CHECK_LAUNCH("gather_rows");
     return 0;
 }
 

@@ -52,6 +52,7 @@ class TagenexB200:
         self.f32 = int(dtype == torch.float32)
         self.W, self.V, self.eps = cfg.width, cfg.vocab_size, cfg.eps
         self.use_tc = os.environ.get('P3_LM_TC', '1') != '0'
+        self.moe_dense_rows = int(os.environ.get('P3_LM_MOE_DENSE_ROWS', '1024'))   # (token, choice) pairs from which experts run as dense GEMMs
         self.use_skinny = os.environ.get('P3_LM_SKINNY', '1') != '0' and hasattr(_lib.lib(), 'p3_gemm_skinny')
         w = weights
         mat = lambda t: t.to(self.dev, dtype).contiguous()                     # matrices: the compute type
@@ -259,14 +260,35 @@ class TagenexB200:
         where = torch.empty(n, dtype=torch.int32, device=dev)
         call('p3_moe_sort', ptr(ids), n, f.experts, ptr(seg), ptr(order), ptr(where), st)
         gu = torch.empty((n, 2 * f.ff), dtype=torch.float32, device=dev)
-        ev = self._ev()
-        self.gemm_any(xa, L['gu'], gu, rows=order, row_div=f.top, seg=seg, n_groups=f.experts, M=n)
-        self._ev(ev, 'moe_gemm', 2 * n * 2 * f.ff * self.W, L['gu'].numel() * L['gu'].element_size())
         hid = torch.empty((n, f.ff), dtype=self.dtype, device=dev)
+        dn = torch.empty((n, self.W), dtype=torch.float32, device=dev)
+        # Large batches (prompt portions): the segment offsets are read back (one small D2H per mixture layer) and every expert's
+        # rows go through the tcgen05 GEMM as a dense product over the gathered, expert-ordered activations. Small batches stay
+        # on the device-side grouped kernel, which needs no host knowledge of the counts.
+        dense = (self.use_tc and not self.f32 and n >= self.moe_dense_rows and self.W % 8 == 0 and f.ff % 8 == 0)
+        ev = self._ev()
+        if dense:
+            xs = torch.empty((n, self.W), dtype=self.dtype, device=dev)
+            call('p3_gather_rows', ptr(xa), xa.stride(0), self.f32, ptr(order), f.top, ptr(xs), n, self.W, st)
+            cut = seg.tolist()
+            for ex in range(f.experts):
+                a0, a1 = cut[ex], cut[ex + 1]
+                if a1 > a0:
+                    call('p3_gemm', ptr(xs[a0:a1]), xs.stride(0), ptr(L['gu'][ex]), L['gu'].stride(1), None, ptr(gu[a0:a1]), gu.stride(0),
+                         None, None, a1 - a0, 2 * f.ff, self.W, _lib.EPI_F32, 0, st)
+        else:
+            self.gemm_any(xa, L['gu'], gu, rows=order, row_div=f.top, seg=seg, n_groups=f.experts, M=n)
+        self._ev(ev, 'moe_gemm', 2 * n * 2 * f.ff * self.W, L['gu'].numel() * L['gu'].element_size())
         call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, n, f.ff, f.limit, TagenexConfig.GLU_ALPHA,
              None, st)
-        dn = torch.empty((n, self.W), dtype=torch.float32, device=dev)
         ev = self._ev()
-        self.gemm_any(hid, L['down'], dn, seg=seg, n_groups=f.experts, M=n)
+        if dense:
+            for ex in range(f.experts):
+                a0, a1 = cut[ex], cut[ex + 1]
+                if a1 > a0:
+                    call('p3_gemm', ptr(hid[a0:a1]), hid.stride(0), ptr(L['down'][ex]), L['down'].stride(1), None, ptr(dn[a0:a1]),
+                         dn.stride(0), None, None, a1 - a0, self.W, f.ff, _lib.EPI_F32, 0, st)
+        else:
+            self.gemm_any(hid, L['down'], dn, seg=seg, n_groups=f.experts, M=n)
         self._ev(ev, 'moe_gemm', 2 * n * f.ff * self.W, L['down'].numel() * L['down'].element_size())
         call('p3_moe_combine', ptr(dn), dn.stride(0), ptr(where), ptr(wts), f.top, ptr(y), T, self.W, st)

@@ -416,6 +416,21 @@ def test_router_sort_grouped_products_and_combine(lib, dtype):
     assert (wts.cpu().double()[same] - ow[same]).abs().max() < 1e-5
 
 
+def test_experts_as_dense_products_equal_the_grouped_kernel(lib):
+    """large batches run every expert's rows through the tensor-core GEMM over gathered activations (segment offsets read back);
+    forced here for a small batch and compared with the device-side grouped kernel and the oracle"""
+    configs, weights, engine, tagenex, paged, O = _mods()
+    cfg = configs.tiny_tagenex()
+    model, w = make(cfg, B16, seed=17)
+    toks = tokens(150, cfg['vocab'], 18)
+    grouped = run_schedule(model, toks, [150])
+    model.moe_dense_rows = 1
+    dense = run_schedule(model, toks, [150])
+    assert_close(dense, grouped, B16)
+    assert_close(dense, O.forward(cfg, w, toks, torch.float64), B16)
+    assert float(row_err(dense, grouped).median()) < 5e-3
+
+
 def test_qkv_post_norms_value_mixing_gate_and_cache_write(lib):
     configs, weights, engine, tagenex, paged, O = _mods()
     from phi3_b200._lib import QkvPostArgs, call_struct, ptr
