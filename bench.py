@@ -499,9 +499,11 @@ def run_tagenex(args):
         os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 1590.0
     dev = torch.device('cuda:0')
     sizes = [dict(name='w3072_h32x96_ff8192_L4', width=3072, heads=32, kv=32, dim=96, ff=8192, layers=4, window=1024, moe=False),
+             dict(name='w3072_h32x96_ff8192_L4_b16', width=3072, heads=32, kv=32, dim=96, ff=8192, layers=4, window=1024, moe=False,
+                  batch=16),
              dict(name='w3072_h32x96_kv8_moe_L4', width=3072, heads=32, kv=8, dim=96, ff=8192, layers=4, window=1024, moe=True),
              dict(name='w1024_h8x128_kv2_moe_L4', width=1024, heads=8, kv=2, dim=128, ff=4096, layers=4, window=512, moe=True)]
-    vocab, B, L, CTX_D, NEW_D = 32064, 4, 2048, 2048, 32
+    vocab, L, CTX_D, NEW_D = 32064, 2048, 2048, 32
 
     def timed(fn, n):
         for _ in range(max(3, args.warmup)):
@@ -517,6 +519,7 @@ def run_tagenex(args):
 
     out = []
     for sz in sizes:
+        B = sz.get('batch', 4)
         cfg = _tagenex_cfg(sz['width'], sz['heads'], sz['kv'], sz['dim'], sz['ff'], sz['layers'], sz['window'], vocab, sz['moe'])
         m = TagenexB200(cfg, weights.random_tagenex_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
         g = torch.Generator().manual_seed(0)

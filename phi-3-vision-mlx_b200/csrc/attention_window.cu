@@ -149,22 +149,49 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
 
 // ---------------------------------------------------------------------------------------------------------------------------
 // bf16 serving mode, head sizes that tile (dim % 16 == 0, vdim % 8 == 0, both <= 128): the two products run on the tensor cores
-// (mma.sync m16n8k16, fp32 accumulators). One CTA = up to 64 query rows (4 warps x 16) x one head, key tile = one page. Scores,
-// mask, penalty (staged per tile in shared memory, index row - col + 63), sink and the online softmax stay fp32 in registers; the
-// weights are rounded to bf16 only as the A operand of P.V, taken straight from the score accumulators; V is read with
-// ldmatrix.trans from its row-major page.
+// (mma.sync m16n8k16, fp32 accumulators). One CTA = up to 64 query rows (4 warps x 16) x one head, key tile = one page. The K and
+// V pages and the tile's penalties travel through a two-stage cp.async ring, so page j + 1 is in flight while page j is
+// multiplied. Scores, mask, penalty (index row - col + 63 into the staged slice), sink and the online softmax stay fp32 in
+// registers, in the base-2 domain (scale, penalty and sink carry the factor log2 e, so a weight is one subtraction and one
+// ex2); the weights are rounded to bf16 only as the A operand of P.V, taken straight from the score accumulators. K fragments
+// come by ldmatrix from the row-major page, V by ldmatrix.trans. A page that every row of the tile sees in full (behind the
+// diagonal, inside the window) skips the visibility tests.
 template <int DK, int DN>
-__global__ void __launch_bounds__(128) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
+__global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
     extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr float LOG2E = 1.4426950408889634f;
     const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8;
-    bf16* Ks = reinterpret_cast<bf16*>(smraw);               // [64][ldk]
-    bf16* Vs = Ks + P3_PAGE * ldk;                           // [64][ldv]
-    float* pen_s = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);   // [128]
+    const int stage_elems = P3_PAGE * (ldk + ldv);           // bf16 elements of one stage: K [64][ldk] then V [64][ldv]
+    bf16* kv_s = reinterpret_cast<bf16*>(smraw);
+    float* pen_s = reinterpret_cast<float*>(kv_s + 2 * stage_elems);   // [2][128]
     const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
     const int row0 = tile.x, nq = tile.y, slot = tile.z, pos0 = tile.w;
     const int h = blockIdx.y, g = h / (a.n_heads / a.n_kv);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int r0 = warp * 16 + gid, r1 = r0 + 8;             // this thread's two rows of the tile
+    const int last = pos0 + nq - 1;
+    const int first = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
+    const float* pen = a.penalty ? a.penalty + (size_t)h * a.n_penalty : nullptr;
+    const int kc = d / 8, vc = dv / 8;                       // 16-byte chunks per row
+    const int pg_lo = first / P3_PAGE, pg_hi = last / P3_PAGE;
+
+    auto stage_page = [&](int pg, int st) {                  // all threads: issue the copies of page pg into stage st
+        const int page = bt[pg];
+        const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
+        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
+        bf16* Ks = kv_s + st * stage_elems;
+        bf16* Vs = Ks + P3_PAGE * ldk;
+        for (int i = tid; i < P3_PAGE * kc; i += 128) cp_async16(smem_u32(Ks + (i / kc) * ldk + (i % kc) * 8), kp + i * 8);
+        for (int i = tid; i < P3_PAGE * vc; i += 128) cp_async16(smem_u32(Vs + (i / vc) * ldv + (i % vc) * 8), vp + i * 8);
+        // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63); plain store, made visible by the barrier
+        // that follows the wait for this stage
+        const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
+        pen_s[st * 128 + tid] = (pen && dist >= 0) ? pen[min(dist, a.n_penalty - 1)] * LOG2E : 0.f;
+    };
+    stage_page(pg_lo, 0);
+    cp_async_commit();
+
     const bf16* q = (const bf16*)a.q + (size_t)h * d;
     uint32_t qf[DK][4];
 #pragma unroll
@@ -176,59 +203,70 @@ __global__ void __launch_bounds__(128) attn_window_prefill_mma_kernel(p3_attn_wi
             if (r1 < nq) { const bf16* p = q + (size_t)(row0 + r1) * a.ld_q + c; qf[t][1] = *reinterpret_cast<const uint32_t*>(p); qf[t][3] = *reinterpret_cast<const uint32_t*>(p + 8); }
         }
     }
-    const float sink = a.sink ? a.sink[h] : -FLT_MAX;
+    const float sink = a.sink ? a.sink[h] * LOG2E : -FLT_MAX;
+    const float scale2 = a.scale * LOG2E;
     float m0 = sink, m1 = sink, l0 = (a.sink && tig == 0) ? 1.f : 0.f, l1 = l0;   // row sums are per-thread partials of a quad
     float o[DN][4];
 #pragma unroll
     for (int n = 0; n < DN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    const int last = pos0 + nq - 1;
-    const int first = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
-    const float* pen = a.penalty ? a.penalty + (size_t)h * a.n_penalty : nullptr;
-    const int kc = d / 8, vc = dv / 8;                       // 16-byte chunks per row
-    for (int pg = first / P3_PAGE; pg <= last / P3_PAGE; pg++) {
-        const int page = bt[pg];
-        const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
-        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
-        __syncthreads();
-        for (int i = tid; i < P3_PAGE * kc; i += 128)
-            *reinterpret_cast<uint4*>(Ks + (i / kc) * ldk + (i % kc) * 8) = __ldg(reinterpret_cast<const uint4*>(kp) + i);
-        for (int i = tid; i < P3_PAGE * vc; i += 128)
-            *reinterpret_cast<uint4*>(Vs + (i / vc) * ldv + (i % vc) * 8) = __ldg(reinterpret_cast<const uint4*>(vp) + i);
-        {   // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63)
-            const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
-            pen_s[tid] = (pen && dist >= 0) ? pen[min(dist, a.n_penalty - 1)] : 0.f;
-        }
-        __syncthreads();
+
+    for (int pg = pg_lo; pg <= pg_hi; pg++) {
+        const int st = (pg - pg_lo) & 1;
+        __syncthreads();                                     // every warp is done with the stage that is refilled now
+        if (pg < pg_hi) stage_page(pg + 1, st ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();                                  // page pg has landed (this thread's copies) ...
+        __syncthreads();                                     // ... and everyone else's
+        const bf16* Ks = kv_s + st * stage_elems;
+        const bf16* Vs = Ks + P3_PAGE * ldk;
+        const float* ps = pen_s + st * 128;
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        // K fragments: one ldmatrix.x4 = keys 16 jj .. 16 jj + 15 x dims 16 t .. 16 t + 15 (b0, b1 of key block 2 jj, then 2 jj + 1)
+        const bf16* krow = Ks + ((lane & 7) + 8 * (lane >> 4)) * ldk + 8 * ((lane >> 3) & 1);
 #pragma unroll
         for (int t = 0; t < DK; t++) {
             if (t * 16 < d) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const bf16* kr = Ks + (j * 8 + gid) * ldk + t * 16 + tig * 2;
-                    mma_bf16_16816(s[j], qf[t], *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+                for (int jj = 0; jj < 4; jj++) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3, smem_u32(krow + jj * 16 * ldk + t * 16));
+                    mma_bf16_16816(s[2 * jj], qf[t], b0, b1);
+                    mma_bf16_16816(s[2 * jj + 1], qf[t], b2, b3);
                 }
             }
         }
         float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
+        // every key of the page is visible to every row of the tile: behind the first row, and the last row's window reaches it
+        const bool full = pg * P3_PAGE + 63 <= pos0 && (a.window <= 0 || pos0 + 63 - pg * P3_PAGE < a.window);
+        if (full) {
 #pragma unroll
-        for (int j = 0; j < 8; j++)
+            for (int j = 0; j < 8; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
-                const int dist = pos0 + row - (pg * P3_PAGE + col);
-                const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
-                const float v = vis ? s[j][e] * a.scale - pen_s[row - col + 63] : -FLT_MAX;
-                s[j][e] = v;
-                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-            }
+                for (int e = 0; e < 4; e++) {
+                    const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
+                    const float v = fmaf(s[j][e], scale2, -ps[row - col + 63]);
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
+                    const int dist = pos0 + row - (pg * P3_PAGE + col);
+                    const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
+                    const float v = vis ? fmaf(s[j][e], scale2, -ps[row - col + 63]) : -FLT_MAX;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = __expf(m0 - n0), c1 = __expf(m1 - n1);
+        const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);   // m is finite (sink) or -FLT_MAX: the difference is finite or -inf
         m0 = n0; m1 = n1;
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
@@ -236,7 +274,7 @@ __global__ void __launch_bounds__(128) attn_window_prefill_mma_kernel(p3_attn_wi
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const float v = s[j][e];
-                const float p = v > -FLT_MAX ? __expf(v - ((e < 2) ? n0 : n1)) : 0.f;
+                const float p = (full || v > -FLT_MAX) ? exp2f(v - ((e < 2) ? n0 : n1)) : 0.f;
                 s[j][e] = p;
                 if (e < 2) ps0 += p; else ps1 += p;
             }
@@ -260,6 +298,7 @@ __global__ void __launch_bounds__(128) attn_window_prefill_mma_kernel(p3_attn_wi
             }
         }
     }
+    cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     bf16* out = (bf16*)a.out + (size_t)h * dv;
@@ -428,22 +467,221 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// Decode on the tensor cores (bf16 mode, head sizes that tile). One CTA = one single-token request x one K/V head x one slice of
+// the visible PAGES; its K and V pages stream through a three-stage cp.async ring (whole pages, 16-byte copies), so the kernel
+// is a stream of the cache. The query heads of the group are the rows of one m16n8k16 tile (rows beyond the group are zero).
+// Each warp takes 16 keys of the page: scores by mma.sync from ldmatrix K fragments, fp32 mask / penalty / online softmax in
+// registers (base-2 domain), weights rounded to bf16 as the A operand of P.V against ldmatrix.trans V fragments. The warps keep
+// separate softmax states and are merged through shared memory at the end; slices are merged by attn_window_merge_kernel.
+// Keys of the last page beyond the query's position, and of the first page before the window, are masked; what those cache rows
+// hold is finite (the pool is zero-initialised and only ever written with finite numbers), so a zero weight removes them.
+constexpr int DEC_STAGES = 3;
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+}
+
+// The loop holds no plain global load on its critical path: the penalties of a page's 64 distances travel with the page
+// (4-byte async copies into the stage), and the block-table entry of the page issued next is read one iteration ahead.
+template <int DK, int DN>
+__global__ void __launch_bounds__(128) attn_window_decode_mma_kernel(p3_attn_window_args a) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr float LOG2E = 1.4426950408889634f;
+    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv;
+    const int pr = min(rep, 16);                             // penalty rows per stage
+    const int stage_bytes = P3_PAGE * (ldk + ldv) * 2 + pr * P3_PAGE * 4;   // K [64][ldk], V [64][ldv] (bf16), penalties [pr][64] (fp32)
+    float* Ms = reinterpret_cast<float*>(smraw);             // after the stream: [4 warps][16 rows] maxima, sums, [4][16][dv] vectors
+    float* Ls = Ms + 64;
+    float* Os = Ls + 64;
+    const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
+    const int row = tile.x, slot = tile.z, pos = tile.w;
+    const int g = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+    const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int pg_first = first / P3_PAGE, pg_last = pos / P3_PAGE;
+    const int per = (pg_last - pg_first + n_splits) / n_splits;           // pages per slice, rounded up
+    const int pg_lo = pg_first + split * per, pg_hi = min(pg_last, pg_lo + per - 1);
+    const int n_pg = max(0, pg_hi - pg_lo + 1);
+    const int32_t* bt = a.block_table + (size_t)slot * a.bt_stride;
+    const int kc = d / 8, vc = dv / 8;
+    const float scale2 = a.scale * LOG2E;
+
+    for (int h0 = 0; h0 < rep; h0 += 16) {
+        const int nr = min(16, rep - h0), hb = g * rep + h0;
+        auto stage_page = [&](int pg, int page, int st) {
+            const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * G + g) * P3_PAGE * d;
+            const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * dv;
+            bf16* Ks = reinterpret_cast<bf16*>(smraw + (size_t)st * stage_bytes);
+            bf16* Vs = Ks + P3_PAGE * ldk;
+            for (int i = tid; i < P3_PAGE * kc; i += 128) cp_async16(smem_u32(Ks + (i / kc) * ldk + (i % kc) * 8), kp + i * 8);
+            for (int i = tid; i < P3_PAGE * vc; i += 128) cp_async16(smem_u32(Vs + (i / vc) * ldv + (i % vc) * 8), vp + i * 8);
+            if (a.penalty) {
+                float* Ps = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);
+                for (int i = tid; i < nr * P3_PAGE; i += 128) {
+                    const int dist = pos - (pg * P3_PAGE + (i & 63));             // masked keys (dist < 0) read entry 0, unused
+                    cp_async4(smem_u32(Ps + i), a.penalty + (size_t)(hb + (i >> 6)) * a.n_penalty + min(max(dist, 0), a.n_penalty - 1));
+                }
+            }
+        };
+        __syncthreads();                                     // the merge buffer of the previous pass is read
+#pragma unroll
+        for (int s = 0; s < DEC_STAGES - 1; s++) {
+            if (s < n_pg) stage_page(pg_lo + s, bt[pg_lo + s], s);
+            cp_async_commit();
+        }
+        int next_page = (DEC_STAGES - 1 < n_pg) ? bt[pg_lo + DEC_STAGES - 1] : 0;
+        const bf16* q = (const bf16*)a.q + (size_t)row * a.ld_q + (size_t)hb * d;
+        uint32_t qf[DK][4];
+#pragma unroll
+        for (int t = 0; t < DK; t++) {
+            qf[t][0] = qf[t][1] = qf[t][2] = qf[t][3] = 0u;
+            if (t * 16 < d) {
+                const int c = t * 16 + tig * 2;
+                if (gid < nr) { const bf16* p = q + (size_t)gid * d + c; qf[t][0] = *reinterpret_cast<const uint32_t*>(p); qf[t][2] = *reinterpret_cast<const uint32_t*>(p + 8); }
+                if (gid + 8 < nr) { const bf16* p = q + (size_t)(gid + 8) * d + c; qf[t][1] = *reinterpret_cast<const uint32_t*>(p); qf[t][3] = *reinterpret_cast<const uint32_t*>(p + 8); }
+            }
+        }
+        // the sink enters once per head: as the initial state of slice 0's first warp
+        const bool s0 = split == 0 && warp == 0 && a.sink;
+        float m0 = (s0 && gid < nr) ? a.sink[hb + gid] * LOG2E : -FLT_MAX;
+        float m1 = (s0 && gid + 8 < nr) ? a.sink[hb + gid + 8] * LOG2E : -FLT_MAX;
+        float l0 = (s0 && gid < nr && tig == 0) ? 1.f : 0.f, l1 = (s0 && gid + 8 < nr && tig == 0) ? 1.f : 0.f;
+        const bool has_pen = a.penalty != nullptr;
+        const int prow0 = min(gid, nr - 1) * P3_PAGE, prow1 = min(gid + 8, nr - 1) * P3_PAGE;
+        float o[DN][4];
+#pragma unroll
+        for (int n = 0; n < DN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+        for (int i = 0; i < n_pg; i++) {
+            cp_async_wait<DEC_STAGES - 2>();                 // page i has landed (this thread's copies) ...
+            __syncthreads();                                 // ... and everyone else's; the stage of page i - 1 is free
+            const int ahead = i + DEC_STAGES - 1;
+            if (ahead < n_pg) stage_page(pg_lo + ahead, next_page, ahead % DEC_STAGES);
+            cp_async_commit();
+            if (ahead + 1 < n_pg) next_page = bt[pg_lo + ahead + 1];
+            const int pg = pg_lo + i;
+            const bf16* Ks = reinterpret_cast<const bf16*>(smraw + (size_t)(i % DEC_STAGES) * stage_bytes);
+            const bf16* Vs = Ks + P3_PAGE * ldk;
+            const float* Ps = reinterpret_cast<const float*>(Vs + P3_PAGE * ldv);
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; j++) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            const bf16* krow = Ks + (warp * 16 + (lane & 7) + 8 * (lane >> 4)) * ldk + 8 * ((lane >> 3) & 1);
+#pragma unroll
+            for (int t = 0; t < DK; t++) {
+                if (t * 16 < d) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(b0, b1, b2, b3, smem_u32(krow + t * 16));
+                    mma_bf16_16816(s[0], qf[t], b0, b1);
+                    mma_bf16_16816(s[1], qf[t], b2, b3);
+                }
+            }
+            float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int col = warp * 16 + j * 8 + tig * 2 + (e & 1);
+                    const int kpos = pg * P3_PAGE + col, dist = pos - kpos;
+                    const bool vis = kpos >= first && dist >= 0 && ((e < 2) ? gid : gid + 8) < nr;
+                    float v = -FLT_MAX;
+                    if (vis) v = fmaf(s[j][e], scale2, has_pen ? -LOG2E * Ps[((e < 2) ? prow0 : prow1) + col] : 0.f);
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
+            m0 = n0; m1 = n1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float v = s[j][e];
+                    const float p = v > -FLT_MAX ? exp2f(v - ((e < 2) ? n0 : n1)) : 0.f;
+                    s[j][e] = p;
+                    if (e < 2) ps0 += p; else ps1 += p;
+                }
+            l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+#pragma unroll
+            for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
+            const bf16* vrow = Vs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + 8 * (lane >> 4);
+#pragma unroll
+            for (int n = 0; n < DN; n += 2) {
+                if (n * 8 < dv) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vrow + n * 8));
+                    mma_bf16_16816(o[n], pa, b0, b1);
+                    if (n + 1 < DN) mma_bf16_16816(o[n + 1], pa, b2, b3);
+                }
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                     // the ring is drained and read: its memory becomes the merge buffer
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (tig == 0) {
+            Ms[warp * 16 + gid] = m0; Ms[warp * 16 + gid + 8] = m1;
+            Ls[warp * 16 + gid] = l0; Ls[warp * 16 + gid + 8] = l1;
+        }
+#pragma unroll
+        for (int n = 0; n < DN; n++) {
+            const int c = n * 8 + tig * 2;
+            if (c < dv) {
+                float* w0 = Os + (size_t)(warp * 16 + gid) * dv + c;
+                float* w1 = Os + (size_t)(warp * 16 + gid + 8) * dv + c;
+                w0[0] = o[n][0]; w0[1] = o[n][1]; w1[0] = o[n][2]; w1[1] = o[n][3];
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < nr * dv; i += 128) {
+            const int r = i / dv, c = i % dv;
+            float M = -FLT_MAX;
+#pragma unroll
+            for (int w = 0; w < 4; w++) M = fmaxf(M, Ms[w * 16 + r]);
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float f = Ls[w * 16 + r] > 0.f ? exp2f(Ms[w * 16 + r] - M) : 0.f;
+                L = fmaf(Ls[w * 16 + r], f, L);
+                acc = fmaf(Os[(size_t)(w * 16 + r) * dv + c], f, acc);
+            }
+            if (n_splits == 1) {
+                const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
+                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / L : 0.f);
+            } else {
+                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (dv + 2);
+                if (c == 0) { w[0] = M; w[1] = L; }
+                w[2 + c] = acc;
+            }
+        }
+    }
+}
+
 // combine the slices of one (request, head): out = gate * sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M)
+// (base2: the slices' maxima are in the base-2 domain, as the tensor-core decode kernel keeps them)
 template <typename AT>
-__global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits) {
+__global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, int base2) {
+    auto ex = [base2](float x) { return base2 ? exp2f(x) : expf(x); };
     const int t = blockIdx.x / a.n_heads, h = blockIdx.x % a.n_heads, dv = a.vdim;
     const int row = reinterpret_cast<const int4*>(a.tiles)[t].x;
     const float* w = a.ws + ((size_t)t * a.n_heads + h) * n_splits * (dv + 2);
     float M = -FLT_MAX;
     for (int s = 0; s < n_splits; s++) M = fmaxf(M, w[(size_t)s * (dv + 2)]);
     float L = 0.f;
-    for (int s = 0; s < n_splits; s++) { const float ls = w[(size_t)s * (dv + 2) + 1]; if (ls > 0.f) L = fmaf(ls, expf(w[(size_t)s * (dv + 2)] - M), L); }
+    for (int s = 0; s < n_splits; s++) { const float ls = w[(size_t)s * (dv + 2) + 1]; if (ls > 0.f) L = fmaf(ls, ex(w[(size_t)s * (dv + 2)] - M), L); }
     const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + h] : 1.f;
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float o = 0.f;
         for (int s = 0; s < n_splits; s++) {
             const float ls = w[(size_t)s * (dv + 2) + 1];
-            if (ls > 0.f) o = fmaf(w[(size_t)s * (dv + 2) + 2 + c], expf(w[(size_t)s * (dv + 2)] - M), o);
+            if (ls > 0.f) o = fmaf(w[(size_t)s * (dv + 2) + 2 + c], ex(w[(size_t)s * (dv + 2)] - M), o);
         }
         stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / L : 0.f);
     }
@@ -492,7 +730,7 @@ int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
          attn_window_decode_kernel<AT, CT, NV><<<grid, DW * 32, bytes, st>>>(*a); } while (0)
     if (cv <= 1) GO(1); else if (cv <= 2) GO(2); else if (cv <= 4) GO(4); else GO(8);
 #undef GO
-    if (ns > 1) attn_window_merge_kernel<AT><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns);
+    if (ns > 1) attn_window_merge_kernel<AT><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns, 0);
     return 0;
 }
 }  // namespace
@@ -506,7 +744,7 @@ static bool prefill_mma_ok(const p3_attn_window_args* a) {
 }
 
 static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
-    const size_t bytes = sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + 128 * sizeof(float);
+    const size_t bytes = 2 * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + 128 * sizeof(float));   // two stages
     const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads);
     if (a->dim <= 64 && a->vdim <= 64) {
         if (set_smem(attn_window_prefill_mma_kernel<4, 8>, bytes, "attn_window_prefill")) return -1;
@@ -515,6 +753,22 @@ static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
         if (set_smem(attn_window_prefill_mma_kernel<8, 16>, bytes, "attn_window_prefill")) return -1;
         attn_window_prefill_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a);
     }
+    return 0;
+}
+
+static int launch_decode_mma(const p3_attn_window_args* a, cudaStream_t st) {
+    const int rep = a->n_heads / a->n_kv, pr = rep < 16 ? rep : 16;
+    const size_t bytes = DEC_STAGES * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + sizeof(float) * P3_PAGE * (size_t)pr);
+    const int ns = a->n_splits > 1 ? a->n_splits : 1;
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
+    if (a->dim <= 64 && a->vdim <= 64) {
+        if (set_smem(attn_window_decode_mma_kernel<4, 8>, bytes, "attn_window_decode")) return -1;
+        attn_window_decode_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a);
+    } else {
+        if (set_smem(attn_window_decode_mma_kernel<8, 16>, bytes, "attn_window_decode")) return -1;
+        attn_window_decode_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a);
+    }
+    if (ns > 1) attn_window_merge_kernel<bf16><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns, 1);
     return 0;
 }
 
@@ -536,7 +790,8 @@ extern "C" int p3_attn_window_decode(const p3_attn_window_args* a, cudaStream_t 
     P3_CHECK_ARG(a->n_splits <= 1 || a->ws, "attn_window_decode: several key slices need the workspace");
     P3_CHECK_ARG(a->n_splits <= 65535, "attn_window_decode: too many key slices");
     if (a->n_tiles == 0) return 0;
-    const int rc = a->act_f32 ? launch_decode<float, float>(a, st) : launch_decode<bf16, bf16>(a, st);
+    const int rc = prefill_mma_ok(a) ? launch_decode_mma(a, st)
+                 : a->act_f32 ? launch_decode<float, float>(a, st) : launch_decode<bf16, bf16>(a, st);
     if (rc) return rc;
     P3_CHECK_LAUNCH("attn_window_decode");
     return 0;

@@ -118,15 +118,26 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     }
     float acc[2][4][4] = {};
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int k0 = 0; k0 < p.K; k0 += TK) {
+    // register double buffering: the next k-slab's global loads are in flight while this one is multiplied
+    uint4 ra[2], rb[2];
+    auto fetch = [&](int k0) {
 #pragma unroll
         for (int j = 0; j < 2; j++) {
             const int k = k0 + schunk[j];
             const bool in = k < p.K;                       // K % 8 == 0: a chunk is inside or outside as a whole
-            *reinterpret_cast<uint4*>(&As[srow[j]][schunk[j]]) = (arow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(arow[j] + k)) : zero;
-            *reinterpret_cast<uint4*>(&Bs[srow[j]][schunk[j]]) = (brow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(brow[j] + k)) : zero;
+            ra[j] = (arow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(arow[j] + k)) : zero;
+            rb[j] = (brow[j] && in) ? ldg_nc_v4(brow[j] + k) : zero;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < p.K; k0 += TK) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            *reinterpret_cast<uint4*>(&As[srow[j]][schunk[j]]) = ra[j];
+            *reinterpret_cast<uint4*>(&Bs[srow[j]][schunk[j]]) = rb[j];
         }
         __syncthreads();
+        if (k0 + TK < p.K) fetch(k0 + TK);
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {
             uint32_t a[2][4], b[4][2];

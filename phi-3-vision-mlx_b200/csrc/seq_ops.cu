@@ -29,34 +29,59 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 }
 
 // ---------------------------------------------------------------- embedding -> fp32 residual (+ activation copy)
+// Row kernels below keep up to RPT elements per thread in registers: all loads of a pass are issued before the first use, so a
+// row of a small batch costs a few memory round trips instead of one per loop iteration.
+constexpr int RPT = 8;
+
 template <typename AT>
 __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ x,
                                   AT* __restrict__ xa, int W, int vocab) {
     const int64_t t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float v = __bfloat162float(table[(size_t)id * W + i]);
-        x[(size_t)t * W + i] = v;
-        if (xa) stv(xa + (size_t)t * W + i, v);
+    const bf16* src = table + (size_t)id * W;
+    for (int i0 = threadIdx.x; i0 < W; i0 += RPT * blockDim.x) {
+        float v[RPT];
+#pragma unroll
+        for (int k = 0; k < RPT; k++) { const int i = i0 + k * blockDim.x; v[k] = i < W ? __bfloat162float(src[i]) : 0.f; }
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            const int i = i0 + k * blockDim.x;
+            if (i < W) { x[(size_t)t * W + i] = v[k]; if (xa) stv(xa + (size_t)t * W + i, v[k]); }
+        }
     }
 }
 
 // ---------------------------------------------------------------- x += rms_norm(y) * gain ; activation copy of the new x
 template <typename AT>
 __global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ ybias,
-                                         const float* __restrict__ gain, float* __restrict__ x, AT* __restrict__ xa, int W, float eps) {
+                                         const float* __restrict__ gain, float* x, AT* __restrict__ xa, int W, float eps) {
     __shared__ float sh[32];
     const int64_t t = blockIdx.x;
     const float* yr = y + (size_t)t * ldy;
+    float* xr = x + (size_t)t * W;
+    const int nt = blockDim.x;
+    float v[RPT];                                            // the first RPT * nt elements of the row stay in registers
     float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = yr[i] + (ybias ? ybias[i] : 0.f); ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; v[k] = i < W ? yr[i] + (ybias ? ybias[i] : 0.f) : 0.f; }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) ss = fmaf(v[k], v[k], ss);
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) { const float u = yr[i] + (ybias ? ybias[i] : 0.f); ss = fmaf(u, u, ss); }
+    float xv[RPT], gv[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; xv[k] = i < W ? xr[i] : 0.f; gv[k] = i < W ? gain[i] : 0.f; }
     ss = block_sum(ss, sh);
     const float r = 1.0f / sqrtf(ss / (float)W + eps);
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float v = x[(size_t)t * W + i] + (yr[i] + (ybias ? ybias[i] : 0.f)) * r * gain[i];
-        x[(size_t)t * W + i] = v;
-        if (xa) stv(xa + (size_t)t * W + i, v);
+#pragma unroll
+    for (int k = 0; k < RPT; k++) {
+        const int i = threadIdx.x + k * nt;
+        if (i < W) { const float u = xv[k] + v[k] * r * gv[k]; xr[i] = u; if (xa) stv(xa + (size_t)t * W + i, u); }
+    }
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) {
+        const float u = xr[i] + (yr[i] + (ybias ? ybias[i] : 0.f)) * r * gain[i];
+        xr[i] = u;
+        if (xa) stv(xa + (size_t)t * W + i, u);
     }
 }
 
@@ -67,15 +92,24 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* 
     __shared__ float sh[32];
     const int64_t r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * W;
+    const int nt = blockDim.x;
+    float v[RPT], gv[RPT];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; v[k] = i < W ? xr[i] : 0.f; gv[k] = i < W ? gain[i] : 0.f; }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) ss = fmaf(v[k], v[k], ss);
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) { const float u = xr[i]; ss = fmaf(u, u, ss); }
     ss = block_sum(ss, sh);
     const float s = 1.0f / sqrtf(ss / (float)W + eps);
-    for (int i = threadIdx.x; i < W; i += blockDim.x) stv(out + (size_t)r * W + i, xr[i] * s * gain[i]);
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; if (i < W) stv(out + (size_t)r * W + i, v[k] * s * gv[k]); }
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) stv(out + (size_t)r * W + i, xr[i] * s * gain[i]);
 }
 
 // ---------------------------------------------------------------- per-head q/k norm + value mixing + gate + paged K/V write
-// One CTA per token, one warp per head job: H query heads, G key heads, G value heads, then the H gate logits.
+// Grid (token, job group): one warp per head job (H query heads, G key heads, G value heads); group 0 also turns the H gate
+// logits into gates. A head's numbers stay in registers between the statistic and the write (head sizes <= 256: 8 per lane).
 template <typename AT, typename CT>
 __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -83,37 +117,53 @@ __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
     const int slot = a.tok_slot[t], pos = a.tok_pos[t];
     const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
     const int H = a.n_heads, G = a.n_kv, d = a.dim, dv = a.vdim;
-    for (int job = warp; job < H + 2 * G; job += nw) {
+    for (int job = blockIdx.y * nw + warp; job < H + 2 * G; job += gridDim.y * nw) {
         if (job < H + G) {                                   // query or key head: RMS norm over its d numbers, shared gain
             const bool isq = job < H;
             const int h = isq ? job : job - H;
             const float* src = pr + (isq ? a.q_off : a.k_off) + (size_t)h * d;
             const float* gain = isq ? a.q_gain : a.k_gain;
+            float sv[8], gv[8];
             float ss = 0.f;
-            for (int i = lane; i < d; i += 32) ss = fmaf(src[i], src[i], ss);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { const int i = lane + 32 * k; sv[k] = i < d ? src[i] : 0.f; gv[k] = i < d ? gain[i] : 0.f; }
+#pragma unroll
+            for (int k = 0; k < 8; k++) ss = fmaf(sv[k], sv[k], ss);
             ss = warp_sum(ss);
             const float r = 1.0f / sqrtf(ss / (float)d + a.eps);
             if (isq) {
                 AT* dst = (AT*)a.q_out + (size_t)t * a.ld_q + (size_t)h * d;
-                for (int i = lane; i < d; i += 32) stv(dst + i, src[i] * r * gain[i]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) { const int i = lane + 32 * k; if (i < d) stv(dst + i, sv[k] * r * gv[k]); }
             } else {
                 CT* dst = (CT*)a.k_pool + (((size_t)page * G + h) * P3_PAGE + off) * d;
-                for (int i = lane; i < d; i += 32) stv(dst + i, src[i] * r * gain[i]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) { const int i = lane + 32 * k; if (i < d) stv(dst + i, sv[k] * r * gv[k]); }
             }
         } else {                                             // value head: v, or (1 - lam) v + lam v_first; the mixed v is cached
             const int h = job - H - G;
             const float* src = pr + a.v_off + (size_t)h * dv;
             float* vf = a.v_first ? a.v_first + (size_t)t * G * dv + (size_t)h * dv : nullptr;
             CT* dst = (CT*)a.v_pool + (((size_t)page * G + h) * P3_PAGE + off) * dv;
-            for (int i = lane; i < dv; i += 32) {
-                float v = src[i];
+            float sv[8], fv[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = lane + 32 * k;
+                sv[k] = i < dv ? src[i] : 0.f;
+                fv[k] = (i < dv && a.v_mode == 2) ? vf[i] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int i = lane + 32 * k;
+                if (i >= dv) continue;
+                float v = sv[k];
                 if (a.v_mode == 1) vf[i] = v;
-                else if (a.v_mode == 2) v = (1.0f - a.v_lambda) * v + a.v_lambda * vf[i];
+                else if (a.v_mode == 2) v = (1.0f - a.v_lambda) * v + a.v_lambda * fv[k];
                 stv(dst + i, v);
             }
         }
     }
-    if (a.gate_out)
+    if (a.gate_out && blockIdx.y == 0)
         for (int h = threadIdx.x; h < H; h += blockDim.x)
             a.gate_out[(size_t)t * H + h] = 1.0f / (1.0f + expf(-pr[a.g_off + h]));
 }
@@ -132,31 +182,42 @@ __global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT*
 }
 
 // ---------------------------------------------------------------- router: fp32 logits, top-k (ties: lower index), softmax over the chosen
+// One CTA per token: the threads split the token's activations, eight experts per pass; partial sums are reduced in an order
+// fixed by the thread layout (lanes, then warps in ascending order), so a token's logits do not depend on the batch.
 template <typename AT>
 __global__ void router_topk_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr, const float* __restrict__ br,
                                    int T, int W, int E, int top, int32_t* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float z_all[];                         // [warps][E]
+    extern __shared__ float z[];                             // [E] logits, then [warps][8] partial sums
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int t = blockIdx.x * nw + warp;
-    if (t >= T) return;
-    float* z = z_all + (size_t)warp * E;
+    const int t = blockIdx.x;
+    float* part = z + E;
     const AT* xr = x + (size_t)t * ldx;
     for (int e0 = 0; e0 < E; e0 += 8) {                      // eight experts per pass over the token's activations
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int i = lane; i < W; i += 32) {
+        const int ne = min(8, E - e0);
+#pragma unroll 2
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
             const float xv = ldv(xr + i);
+            float wv[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (e0 + j < E) s[j] = fmaf(xv, Wr[(size_t)(e0 + j) * W + i], s[j]);
+            for (int j = 0; j < 8; j++) wv[j] = j < ne ? Wr[(size_t)(e0 + j) * W + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[j] = fmaf(xv, wv[j], s[j]);
         }
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const float t = warp_sum(s[j]);
-            if (lane == 0 && e0 + j < E) z[e0 + j] = t + br[e0 + j];
+            const float v = warp_sum(s[j]);
+            if (lane == 0) part[warp * 8 + j] = v;
         }
+        __syncthreads();
+        if (threadIdx.x < ne) {
+            float v = 0.f;
+            for (int w = 0; w < nw; w++) v += part[w * 8 + threadIdx.x];
+            z[e0 + threadIdx.x] = v + br[e0 + threadIdx.x];
+        }
+        __syncthreads();
     }
-    __syncwarp();
-    if (lane == 0) {
+    if (threadIdx.x == 0) {
         float zmax = 0.f, den = 0.f;
         for (int j = 0; j < top; j++) {
             int best = -1; float bv = 0.f;
@@ -220,10 +281,15 @@ __global__ void gather_rows_kernel(const AT* __restrict__ x, int64_t ldx, const 
 // ---------------------------------------------------------------- out[t] = sum_j w[t][j] * y[where[t * top + j]]   (j ascending)
 __global__ void moe_combine_kernel(const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ where,
                                    const float* __restrict__ wts, int top, float* __restrict__ out, int W) {
+    extern __shared__ float cw[];                            // [top] weights, then [top] sorted rows
+    int* rows = reinterpret_cast<int*>(cw + top);
     const int64_t t = blockIdx.x;
+    for (int j = threadIdx.x; j < top; j += blockDim.x) { cw[j] = wts[t * top + j]; rows[j] = where[t * top + j]; }
+    __syncthreads();
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float s = 0.f;
-        for (int j = 0; j < top; j++) s = fmaf(wts[t * top + j], y[(size_t)where[t * top + j] * ldy + i], s);
+#pragma unroll 4
+        for (int j = 0; j < top; j++) s = fmaf(cw[j], y[(size_t)rows[j] * ldy + i], s);
         out[(size_t)t * W + i] = s;
     }
 }
@@ -248,7 +314,7 @@ extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x
 extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_bias, const float* gain, float* x, void* x_act, int act_f32,
                                     int64_t T, int W, float eps, cudaStream_t st) {
     if (T == 0) return 0;
-    const int th = W >= 1024 ? 256 : 128;
+    const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;     // the row fits the threads' registers up to W = 8192
     if (act_f32) postnorm_residual_kernel<float><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (float*)x_act, W, eps);
     else postnorm_residual_kernel<bf16><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (bf16*)x_act, W, eps);
     P3_CHECK_LAUNCH("postnorm_residual");
@@ -258,7 +324,7 @@ extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_
 extern "C" int p3_rmsnorm_rows_f32(const float* x, const int32_t* rows, const float* gain, void* out, int out_f32, int64_t R, int W,
                                    float eps, cudaStream_t st) {
     if (R == 0) return 0;
-    const int th = W >= 1024 ? 256 : 128;
+    const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;
     if (out_f32) rmsnorm_rows_kernel<float><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (float*)out, W, eps);
     else rmsnorm_rows_kernel<bf16><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (bf16*)out, W, eps);
     P3_CHECK_LAUNCH("rmsnorm_rows_f32");
@@ -269,10 +335,13 @@ extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a && a->proj && a->q_out && a->k_pool && a->v_pool && a->block_table && a->tok_slot && a->tok_pos, "qkv_post: null argument");
     P3_CHECK_ARG(a->v_mode == 0 || a->v_first, "qkv_post: value mixing needs the v_first buffer");
     if (a->T == 0) return 0;
-    const int jobs = a->n_heads + 2 * a->n_kv;
-    const int th = jobs >= 8 ? 256 : 128;
-    if (a->act_f32 && a->cache_f32) qk_norm_kv_write_kernel<float, float><<<a->T, th, 0, st>>>(*a);
-    else if (!a->act_f32 && !a->cache_f32) qk_norm_kv_write_kernel<bf16, bf16><<<a->T, th, 0, st>>>(*a);
+    P3_CHECK_ARG(a->dim <= 256 && a->vdim <= 256, "qkv_post: head sizes must be <= 256");
+    const int jobs = a->n_heads + 2 * a->n_kv, th = 128;
+    // few tokens: one warp per job; many tokens: each CTA walks several jobs (the grid is large enough already)
+    const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
+    const dim3 grid((unsigned)a->T, (unsigned)groups);
+    if (a->act_f32 && a->cache_f32) qk_norm_kv_write_kernel<float, float><<<grid, th, 0, st>>>(*a);
+    else if (!a->act_f32 && !a->cache_f32) qk_norm_kv_write_kernel<bf16, bf16><<<grid, th, 0, st>>>(*a);
     else P3_CHECK_ARG(false, "qkv_post: activations and cache must both be fp32 or both bf16");
     P3_CHECK_LAUNCH("qkv_post");
     return 0;
@@ -293,11 +362,10 @@ extern "C" int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float
                               int32_t* ids, float* wts, cudaStream_t st) {
     P3_CHECK_ARG(top >= 1 && top <= E && E <= 1024, "router_topk: need 1 <= top <= experts <= 1024");
     if (T == 0) return 0;
-    const int nw = 4;
-    const unsigned grid = (unsigned)((T + nw - 1) / nw);
-    const size_t sm = (size_t)nw * E * sizeof(float);
-    if (x_f32) router_topk_kernel<float><<<grid, nw * 32, sm, st>>>((const float*)x, ldx, Wr, br, T, W, E, top, ids, wts);
-    else router_topk_kernel<bf16><<<grid, nw * 32, sm, st>>>((const bf16*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    const int nw = W >= 1024 ? 8 : 4;
+    const size_t sm = ((size_t)E + nw * 8) * sizeof(float);
+    if (x_f32) router_topk_kernel<float><<<(unsigned)T, nw * 32, sm, st>>>((const float*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    else router_topk_kernel<bf16><<<(unsigned)T, nw * 32, sm, st>>>((const bf16*)x, ldx, Wr, br, T, W, E, top, ids, wts);
     P3_CHECK_LAUNCH("router_topk");
     return 0;
 }
@@ -322,7 +390,7 @@ extern "C" int p3_gather_rows(const void* x, int64_t ldx, int x_f32, const int32
 extern "C" int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const float* wts, int top, float* out, int64_t T, int W,
                               cudaStream_t st) {
     if (T == 0) return 0;
-    moe_combine_kernel<<<(unsigned)T, 128, 0, st>>>(y, ldy, where, wts, top, out, W);
+    moe_combine_kernel<<<(unsigned)T, W >= 1024 ? 256 : 128, (size_t)top * 8, st>>>(y, ldy, where, wts, top, out, W);
     P3_CHECK_LAUNCH("moe_combine");
     return 0;
 }

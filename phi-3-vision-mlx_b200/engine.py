@@ -15,6 +15,8 @@ row ends. This engine serves a stream of requests instead:
 
 A model plugs in with kv_layout(), cache_dtype(), prepare(max_context) and forward(StepBatch, pool) (tagenex.TagenexB200).
 """
+import os
+
 import numpy as np
 import torch
 from . import _lib
@@ -36,6 +38,12 @@ class Engine:
         self.q_tile = int(getattr(model, 'q_tile', 32))      # query rows per CTA of the model's prefill attention kernel
         self.slot_of = {}                                    # request id -> slot
         self.steps = 0
+        # decode-only steps (every entry brings one token) are captured as CUDA graphs, keyed by what fixes their launches: the
+        # number of requests, of wanted rows, and the 128-key bucket of the longest context (it sets the key slices of the decode
+        # attention). A key runs eagerly the first time it is seen, is captured the second time and replayed from then on; the
+        # step's descriptors are copied into the graph's static buffer before each replay.
+        self.use_graphs = os.environ.get('P3_LM_GRAPH', '1') != '0' and self.dev.type == 'cuda'
+        self._graphs = {}
 
     # ------------------------------------------------------------------ sequence table
     def length(self, rid):
@@ -102,6 +110,16 @@ class Engine:
         pad = (-3 * T) % 4                                   # tile records are read as 16-byte vectors
         flat = np.concatenate([flat[:3 * T], np.zeros(pad, np.int32), flat[3 * T:]])
         d = torch.from_numpy(flat).to(self.dev)
+        self._bind(b, d)
+        pool.sync()
+        return b
+
+    @staticmethod
+    def _bind(b, d):
+        """point the batch's descriptor views into the flat int32 buffer d"""
+        T = b.T
+        pad = (-3 * T) % 4
+        b.flat = d
         b.ids, b.tok_slot, b.tok_pos = d[:T], d[T:2 * T], d[2 * T:3 * T]
         o = 3 * T + pad
         b.pf_tiles = d[o:o + 4 * b.n_pf]
@@ -109,19 +127,48 @@ class Engine:
         b.dec_tiles = d[o:o + 4 * b.n_dec]
         o += 4 * b.n_dec
         b.want_rows = d[o:o + b.R]
-        pool.sync()
-        return b
 
     def step(self, entries, end=(), trace=None):
         """-> fp32 logits [number of wanted rows, vocab] on the device (None if nothing is wanted), rows in the order of the
         entries and of their wanted indices"""
         b = self.build_batch(entries)
-        logits = self.model.forward(b, self.pool, trace=trace) if b.T else None
+        if not b.T:
+            logits = None
+        elif (self.use_graphs and trace is None and b.n_pf == 0 and getattr(self.model, 'profile', None) is None
+              and getattr(self.model, 'graph_safe', lambda batch: False)(b)):
+            logits = self._graph_step(b)
+        else:
+            logits = self.model.forward(b, self.pool, trace=trace)
         for rid in end:
             if rid in self.slot_of:
                 self.finish(rid)
         self.steps += 1
         return logits
+
+
+    def _graph_step(self, b):
+        from .model import capture_graph
+        key = (b.n_dec, b.R, -(-(b.max_pos + 1) // 128))
+        ent = self._graphs.get(key)
+        if ent is None:
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = {}
+            return self.model.forward(b, self.pool)
+        if 'graph' not in ent:
+            sb = StepBatch()
+            sb.T, sb.n_pf, sb.n_dec, sb.R, sb.max_pos = b.T, 0, b.n_dec, b.R, b.max_pos
+            self._bind(sb, torch.empty_like(b.flat))
+            sb.flat.copy_(b.flat)
+            torch.cuda.synchronize()
+            ent['graph'] = torch.cuda.CUDAGraph()
+            with capture_graph(ent['graph']):
+                ent['out'] = self.model.forward(sb, self.pool)
+            ent['batch'] = sb
+        else:
+            ent['batch'].flat.copy_(b.flat)
+        ent['graph'].replay()
+        return None if ent['out'] is None else ent['out'].clone()
 
 
 class _Seq:

@@ -34,7 +34,7 @@ def _stream():
 
 class StepBatch:
     """Device-side description of one engine step (built by engine.Engine.step)."""
-    __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos')
+    __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos', 'flat')
 
 
 class TagenexB200:
@@ -71,6 +71,7 @@ class TagenexB200:
             L['lam'] = float(w[a + 'vmix'].float()) if m.v_role == 'mix' else 0.0
             L['o'] = mat(w[a + 'o'])
             L['pen'] = None
+            L['mma'] = bool(_lib.ATTN_WINDOW_MMA and not self.f32 and m.dim % 16 == 0 and m.vdim % 8 == 0 and m.dim <= 128 and m.vdim <= 128)
             f = lc.ff
             if f is not None:
                 L['norm2'] = f32(w[p + 'norm2'])
@@ -88,9 +89,7 @@ class TagenexB200:
         self._pen_len = 0
         # query rows per attention tile the engine cuts prompt portions into: 64 when every layer takes the tensor-core prefill
         # kernel (bf16, key size % 16 == 0, value size % 8 == 0, both <= 128; csrc/attention_window.cu), else 32
-        mma = _lib.ATTN_WINDOW_MMA and not self.f32 and all(
-            l.mixer.dim % 16 == 0 and l.mixer.vdim % 8 == 0 and l.mixer.dim <= 128 and l.mixer.vdim <= 128 for l in cfg.layers)
-        self.q_tile = 64 if mma else 32
+        self.q_tile = 64 if all(L['mma'] for L in self.layers) else 32
         self.profile = None      # bench.py: list of (kind, ev0, ev1, flops, bytes) when instrumenting
 
     def _ev(self, start=None, kind=None, flops=0, nbytes=0):
@@ -123,28 +122,37 @@ class TagenexB200:
                 call('p3_distance_penalty_table', ptr(L['r1']), ptr(L['r2']), ptr(L['pen']), m.heads, n, _stream())
         self._pen_len = max_context
 
+    def graph_safe(self, b):
+        """may this step be captured as a CUDA graph? Not when a mixture layer would read its segment offsets back."""
+        return all(l.ff is None or l.ff.kind != 'moe' or b.T * l.ff.top < self.moe_dense_rows or self.f32 or not self.use_tc
+                   for l in self.cfg.layers)
+
     # ------------------------------------------------------------------ matrix products
-    def linear(self, x, w, out, bias32=None, bias16=None):
+    def linear(self, x, w, out, bias32=None, bias16=None, nxt=None):
         """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T (+ bias). Returns the bias (fp32) that is STILL TO ADD: None
         when the product added it, bias32 when the kernel has no bias input (the weight-streaming kernel of small batches); the
-        consumer kernel (activation / output norm) then adds it."""
+        consumer kernel (activation / output norm) then adds it. `nxt`: the matrix of the next product; the weight-streaming
+        kernel pulls its first megabytes into L2 so that they arrive while the small kernels in between run."""
         M, K = x.shape
         N = w.shape[0]
         ev = self._ev()
         try:
-            return self._linear(x, w, out, bias32, bias16)
+            return self._linear(x, w, out, bias32, bias16, nxt)
         finally:
             self._ev(ev, 'gemm', 2 * M * N * K, w.numel() * w.element_size() + x.numel() * x.element_size() + out.numel() * out.element_size())
 
-    def _linear(self, x, w, out, bias32=None, bias16=None):
+    L2_PREFETCH_CAP = int(os.environ.get('P3_LM_PF_CAP_MB', '16')) << 20
+
+    def _linear(self, x, w, out, bias32=None, bias16=None, nxt=None):
         M, K = x.shape
         N = w.shape[0]
         aligned = (not self.f32 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
         if (self.use_skinny and aligned and M <= 16 and K % 64 == 0 and N % 16 == 0 and out.dtype == torch.float32
                 and w.is_contiguous()):
             # <= 16 tokens: the product is a stream of the weights; the Phi-3 decode kernel does that at HBM speed
+            pf = 0 if nxt is None else min(nxt.numel() * nxt.element_size(), self.L2_PREFETCH_CAP)
             call('p3_gemm_skinny', ptr(x), x.stride(0), None, self.eps, ptr(w), ptr(out), out.stride(0), None, M, N, K,
-                 _lib.EPI_F32, None, 0, None, None, 0, _stream())
+                 _lib.EPI_F32, None, 0, None, ptr(nxt) if pf else None, pf, _stream())
             return bias32
         if self.use_tc and aligned and (bias32 is None or bias16 is not None):
             epi = _lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_NONE
@@ -183,7 +191,7 @@ class TagenexB200:
             H, G, d, dv = m.heads, m.kv_heads, m.dim, m.vdim
             nq, nk, nv = H * d, G * d, G * dv
             proj = e(T, nq + nk + nv + H)
-            self.linear(xa, L['qkvg'], proj)
+            self.linear(xa, L['qkvg'], proj, nxt=L['o'])
             q, gate, att = e(T, nq, dt=act), e(T, H), e(T, H * dv, dt=act)
             if m.v_role != 'none' and v_first is None:
                 v_first = e(T, nv)
@@ -214,25 +222,31 @@ class TagenexB200:
                 self._ev(ev, 'attn_prefill', 2 * (T - b.n_dec) * H * span * (d + dv), 0)
             if b.n_dec:
                 w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
-                # slices of the visible keys per request: enough CTAs for eight per SM, at least 128 keys (one pass of a CTA) per slice
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
-                w.n_splits = max(1, min(-(-8 * 148 // (b.n_dec * G)), -(-span // 128)))
+                if L['mma']:
+                    # tensor-core kernel: slices of whole pages, one wave of two CTAs per SM, a slice no shorter than a page
+                    w.n_splits = max(1, min(2 * 148 // (b.n_dec * G), 2 * -(-span // 128)))
+                else:
+                    # one key per lane: enough CTAs for eight per SM, at least 128 keys (one pass of a CTA) per slice
+                    w.n_splits = max(1, min(-(-8 * 148 // (b.n_dec * G)), -(-span // 128)))
                 ws = e(b.n_dec * H * w.n_splits * (dv + 2)) if w.n_splits > 1 else None
                 w.ws = ptr(ws)
                 ev = self._ev()
                 call_struct('p3_attn_window_decode', w, st)
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
                 self._ev(ev, 'attn_decode', 2 * b.n_dec * H * span * (d + dv), b.n_dec * G * span * (d + dv) * esz)
-            self.linear(att, L['o'], y)
+            f = L['cfg'].ff
+            after = self.layers[li + 1]['qkvg'] if li + 1 < len(self.layers) else self.head
+            self.linear(att, L['o'], y, nxt=L['gu'] if f is not None and f.kind == 'dense' else (after if f is None else None))
             call('p3_postnorm_residual', ptr(y), y.stride(0), None, ptr(L['norm1']), ptr(x), ptr(xa), self.f32, T, W, self.eps, st)
             f = L['cfg'].ff
             if f is not None:
                 if f.kind == 'dense':
                     gu, hid = e(T, 2 * f.ff), e(T, f.ff, dt=act)
-                    left = self.linear(xa, L['gu'], gu, L['gu_b32'], L['gu_b16'])
+                    left = self.linear(xa, L['gu'], gu, L['gu_b32'], L['gu_b16'], nxt=L['down'])
                     call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, T, f.ff, f.limit,
                          TagenexConfig.GLU_ALPHA, ptr(left), st)
-                    left = self.linear(hid, L['down'], y, L['down_b32'], L['down_b16'])
+                    left = self.linear(hid, L['down'], y, L['down_b32'], L['down_b16'], nxt=after)
                 else:
                     self._moe(L, f, xa, y, T)
                     left = None

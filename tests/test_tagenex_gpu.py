@@ -199,6 +199,58 @@ def test_first_tokens_and_long_decoding(lib):
     assert rel_err(run_schedule(model, toks, [1]), O.forward(cfg, w, toks, torch.float64)) < TOL[F32]   # all decoded one by one
 
 
+@pytest.mark.parametrize('dtype', [F32, B16])
+def test_captured_decode_steps_equal_eager_steps(lib, dtype):
+    """decode-only steps replay a CUDA graph from their third occurrence on; the logits must be those of eager launches, bit for
+    bit, while requests sit out steps, leave, hand their slot and pages to a newcomer, and the longest context passes a
+    128-key bucket"""
+    configs, weights, engine, tagenex, paged, O = _mods()
+    cfg = configs.tiny_tagenex()
+    model, w = make(cfg, dtype, seed=9)
+    seqs = {k: tokens(n + 24, cfg['vocab'], 50 + i) for i, (k, n) in enumerate({'a': 120, 'b': 5, 'c': 70, 'd': 66}.items())}
+    n_prompt = {'a': 120, 'b': 5, 'c': 70, 'd': 66}
+
+    def run(graphs):
+        eng = engine.Engine(model, 64 * 10, 4)
+        eng.use_graphs = graphs
+        for k in eng.pool.k + eng.pool.v:
+            k.fill_(7.0)
+        got = {k: [] for k in seqs}
+        at = dict(n_prompt)
+
+        def step(names, end=()):
+            entries = []
+            for k in names:
+                n = n_prompt[k] if not got[k] else 1
+                lo = 0 if not got[k] else at[k]
+                entries.append((k, seqs[k][lo:lo + n], [n - 1]))
+                at[k] = lo + n
+            lg = eng.step(entries, end)
+            for i, k in enumerate(names):
+                got[k].append(lg[i:i + 1])
+
+        step(['a', 'b', 'c'])
+        for s in range(20):
+            live = ['a', 'c'] if 8 <= s < 12 else ['a', 'b', 'c']                  # b sits out four steps
+            if s < 15:
+                step(live)
+            elif s == 15:
+                step(live, ['c'])                                                # c leaves ...
+                step(['d'])                                                      # ... and d takes its slot and pages
+            else:
+                step(['a', 'b', 'd'])
+        return {k: torch.cat(v, 0) for k, v in got.items()}, eng
+
+    eager, _ = run(False)
+    replay, eng = run(True)
+    assert any('graph' in g for g in eng._graphs.values()), 'no step was captured'
+    for k in seqs:
+        assert torch.equal(eager[k], replay[k]), k
+        n = eager[k].shape[0]
+        ref = O.forward(cfg, w, seqs[k][:n_prompt[k] + n - 1], torch.float64)[n_prompt[k] - 1:]
+        assert_close(replay[k], ref, dtype, k)
+
+
 def _att(heads, kv, dim, vdim, win, mix, scale=None):
     m = dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=scale or dim ** -0.5, v_mix=mix)
     if win:
@@ -356,6 +408,17 @@ def test_attention_on_the_tensor_cores_and_with_key_slices(lib, shape, window):
         assert (pf.double() - ref).abs().max() < 3e-2 and (dc.double() - ref).abs().max() < 3e-2
     pf, dc, ref = _attention_case(lib, F32, H=6, G=2, d=d, dv=dv, window=window, n_ctx=n, hot=hot, scale=d ** -0.5, n_splits=5)
     assert (pf.double() - ref).abs().max() < 1e-4 and (dc.double() - ref).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize('heads', [(20, 1), (4, 4), (16, 1), (18, 2)])
+def test_tensor_core_decode_with_small_and_large_head_groups(lib, heads):
+    """the query heads of a K/V head are the rows of a 16-row tile: one head, exactly 16, and more than 16 (two passes)"""
+    H, G = heads
+    hot = [(i, i - 69) for i in (70, 128, 199)] + [(i, i - 70) for i in (71, 129, 199)]
+    for splits in (1, 4):
+        pf, dc, ref = _attention_case(lib, B16, H=H, G=G, d=32, dv=48, window=70, n_ctx=200, hot=hot, scale=32 ** -0.5,
+                                      tile_rows=64, n_splits=splits)
+        assert (pf.double() - ref).abs().max() < 3e-2 and (dc.double() - ref).abs().max() < 3e-2
 
 
 def test_attention_sink_takes_weight_but_has_no_value(lib):
