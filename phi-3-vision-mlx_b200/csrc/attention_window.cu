@@ -147,6 +147,17 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     }
 }
 
+// 64 rows of a page (row-major, `chunks` 16-byte pieces per row) -> shared memory rows of pitch ld, by 128 threads: LPR lanes per
+// row (chunks <= LPR), no division in the address arithmetic
+template <int LPR>
+__device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, int chunks, int tid) {
+    const int c = tid % LPR, r0 = tid / LPR;
+    if (c < chunks) {
+#pragma unroll
+        for (int r = r0; r < P3_PAGE; r += 128 / LPR) cp_async16(smem_u32(dst + r * ld + c * 8), src + (r * chunks + c) * 8);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------
 // bf16 serving mode, head sizes that tile (dim % 16 == 0, vdim % 8 == 0, both <= 128): the two products run on the tensor cores
 // (mma.sync m16n8k16, fp32 accumulators). One CTA = up to 64 query rows (4 warps x 16) x one head, key tile = one page. The K and
@@ -182,8 +193,8 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
         const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
         bf16* Ks = kv_s + st * stage_elems;
         bf16* Vs = Ks + P3_PAGE * ldk;
-        for (int i = tid; i < P3_PAGE * kc; i += 128) cp_async16(smem_u32(Ks + (i / kc) * ldk + (i % kc) * 8), kp + i * 8);
-        for (int i = tid; i < P3_PAGE * vc; i += 128) cp_async16(smem_u32(Vs + (i / vc) * ldv + (i % vc) * 8), vp + i * 8);
+        stage_rows<2 * DK>(Ks, ldk, kp, kc, tid);
+        stage_rows<DN>(Vs, ldv, vp, vc, tid);
         // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63); plain store, made visible by the barrier
         // that follows the wait for this stage
         const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
@@ -469,14 +480,26 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
 
 // ---------------------------------------------------------------------------------------------------------------------------
 // Decode on the tensor cores (bf16 mode, head sizes that tile). One CTA = one single-token request x one K/V head x one slice of
-// the visible PAGES; its K and V pages stream through a three-stage cp.async ring (whole pages, 16-byte copies), so the kernel
+// the visible PAGES; its K and V pages stream through a cp.async ring of 2 or 3 stages (whole pages, 16-byte copies; the launch
+// takes as many stages as let two CTAs share an SM), so the kernel
 // is a stream of the cache. The query heads of the group are the rows of one m16n8k16 tile (rows beyond the group are zero).
 // Each warp takes 16 keys of the page: scores by mma.sync from ldmatrix K fragments, fp32 mask / penalty / online softmax in
 // registers (base-2 domain), weights rounded to bf16 as the A operand of P.V against ldmatrix.trans V fragments. The warps keep
 // separate softmax states and are merged through shared memory at the end; slices are merged by attn_window_merge_kernel.
 // Keys of the last page beyond the query's position, and of the first page before the window, are masked; what those cache rows
 // hold is finite (the pool is zero-initialised and only ever written with finite numbers), so a zero weight removes them.
-constexpr int DEC_STAGES = 3;
+constexpr int DEC_MAX_STAGES = 3;                          // a fourth stage measured slower on B200 (two CTAs no longer share an SM)
+
+// wait until at most n of this thread's copy groups are pending (n is uniform over the CTA)
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        default: cp_async_wait<4>(); break;
+    }
+}
 
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
@@ -485,7 +508,7 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 // The loop holds no plain global load on its critical path: the penalties of a page's 64 distances travel with the page
 // (4-byte async copies into the stage), and the block-table entry of the page issued next is read one iteration ahead.
 template <int DK, int DN>
-__global__ void __launch_bounds__(128) attn_window_decode_mma_kernel(p3_attn_window_args a) {
+__global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_window_args a, int n_stages) {
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
     const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv;
@@ -514,8 +537,8 @@ __global__ void __launch_bounds__(128) attn_window_decode_mma_kernel(p3_attn_win
             const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * dv;
             bf16* Ks = reinterpret_cast<bf16*>(smraw + (size_t)st * stage_bytes);
             bf16* Vs = Ks + P3_PAGE * ldk;
-            for (int i = tid; i < P3_PAGE * kc; i += 128) cp_async16(smem_u32(Ks + (i / kc) * ldk + (i % kc) * 8), kp + i * 8);
-            for (int i = tid; i < P3_PAGE * vc; i += 128) cp_async16(smem_u32(Vs + (i / vc) * ldv + (i % vc) * 8), vp + i * 8);
+            stage_rows<2 * DK>(Ks, ldk, kp, kc, tid);
+            stage_rows<DN>(Vs, ldv, vp, vc, tid);
             if (a.penalty) {
                 float* Ps = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);
                 for (int i = tid; i < nr * P3_PAGE; i += 128) {
@@ -525,12 +548,11 @@ __global__ void __launch_bounds__(128) attn_window_decode_mma_kernel(p3_attn_win
             }
         };
         __syncthreads();                                     // the merge buffer of the previous pass is read
-#pragma unroll
-        for (int s = 0; s < DEC_STAGES - 1; s++) {
+        for (int s = 0; s < n_stages - 1; s++) {
             if (s < n_pg) stage_page(pg_lo + s, bt[pg_lo + s], s);
             cp_async_commit();
         }
-        int next_page = (DEC_STAGES - 1 < n_pg) ? bt[pg_lo + DEC_STAGES - 1] : 0;
+        int next_page = (n_stages - 1 < n_pg) ? bt[pg_lo + n_stages - 1] : 0;
         const bf16* q = (const bf16*)a.q + (size_t)row * a.ld_q + (size_t)hb * d;
         uint32_t qf[DK][4];
 #pragma unroll
@@ -554,14 +576,14 @@ __global__ void __launch_bounds__(128) attn_window_decode_mma_kernel(p3_attn_win
         for (int n = 0; n < DN; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
         for (int i = 0; i < n_pg; i++) {
-            cp_async_wait<DEC_STAGES - 2>();                 // page i has landed (this thread's copies) ...
+            cp_async_wait_pending(n_stages - 2);             // page i has landed (this thread's copies) ...
             __syncthreads();                                 // ... and everyone else's; the stage of page i - 1 is free
-            const int ahead = i + DEC_STAGES - 1;
-            if (ahead < n_pg) stage_page(pg_lo + ahead, next_page, ahead % DEC_STAGES);
+            const int ahead = i + n_stages - 1;
+            if (ahead < n_pg) stage_page(pg_lo + ahead, next_page, ahead % n_stages);
             cp_async_commit();
             if (ahead + 1 < n_pg) next_page = bt[pg_lo + ahead + 1];
             const int pg = pg_lo + i;
-            const bf16* Ks = reinterpret_cast<const bf16*>(smraw + (size_t)(i % DEC_STAGES) * stage_bytes);
+            const bf16* Ks = reinterpret_cast<const bf16*>(smraw + (size_t)(i % n_stages) * stage_bytes);
             const bf16* Vs = Ks + P3_PAGE * ldk;
             const float* Ps = reinterpret_cast<const float*>(Vs + P3_PAGE * ldv);
             float s[2][4];
@@ -672,16 +694,19 @@ __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, in
     const int t = blockIdx.x / a.n_heads, h = blockIdx.x % a.n_heads, dv = a.vdim;
     const int row = reinterpret_cast<const int4*>(a.tiles)[t].x;
     const float* w = a.ws + ((size_t)t * a.n_heads + h) * n_splits * (dv + 2);
-    float M = -FLT_MAX;
-    for (int s = 0; s < n_splits; s++) M = fmaxf(M, w[(size_t)s * (dv + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < n_splits; s++) { const float ls = w[(size_t)s * (dv + 2) + 1]; if (ls > 0.f) L = fmaf(ls, ex(w[(size_t)s * (dv + 2)] - M), L); }
     const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + h] : 1.f;
+    float M = -FLT_MAX;
+#pragma unroll 4
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, w[(size_t)s * (dv + 2)]);
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-        float o = 0.f;
+        float L = 0.f, o = 0.f;                              // every thread forms the denominator itself: the loads of all slices are independent
+#pragma unroll 4
         for (int s = 0; s < n_splits; s++) {
-            const float ls = w[(size_t)s * (dv + 2) + 1];
-            if (ls > 0.f) o = fmaf(w[(size_t)s * (dv + 2) + 2 + c], ex(w[(size_t)s * (dv + 2)] - M), o);
+            const float* ws = w + (size_t)s * (dv + 2);
+            const float ms = ws[0], ls = ws[1], os = ws[2 + c];
+            const float f = ls > 0.f ? ex(ms - M) : 0.f;
+            L = fmaf(ls, f, L);
+            o = fmaf(os, f, o);
         }
         stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)h * dv + c, L > 0.f ? o * gate / L : 0.f);
     }
@@ -758,15 +783,19 @@ static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
 
 static int launch_decode_mma(const p3_attn_window_args* a, cudaStream_t st) {
     const int rep = a->n_heads / a->n_kv, pr = rep < 16 ? rep : 16;
-    const size_t bytes = DEC_STAGES * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + sizeof(float) * P3_PAGE * (size_t)pr);
+    const size_t stage = sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + sizeof(float) * P3_PAGE * (size_t)pr;
+    // as many stages as leave room for two CTAs per SM (227 KB, 1 KB reserved per CTA); the merge buffer fits two stages
+    int nst = (int)((227 * 1024 / 2 - 1024) / stage);
+    nst = nst < 2 ? 2 : (nst > DEC_MAX_STAGES ? DEC_MAX_STAGES : nst);
+    const size_t bytes = nst * stage;
     const int ns = a->n_splits > 1 ? a->n_splits : 1;
     const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
     if (a->dim <= 64 && a->vdim <= 64) {
         if (set_smem(attn_window_decode_mma_kernel<4, 8>, bytes, "attn_window_decode")) return -1;
-        attn_window_decode_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a);
+        attn_window_decode_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a, nst);
     } else {
         if (set_smem(attn_window_decode_mma_kernel<8, 16>, bytes, "attn_window_decode")) return -1;
-        attn_window_decode_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a);
+        attn_window_decode_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a, nst);
     }
     if (ns > 1) attn_window_merge_kernel<bf16><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns, 1);
     return 0;

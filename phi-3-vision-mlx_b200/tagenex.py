@@ -32,6 +32,19 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+def _page_slices(pairs, pages, slots=2 * 148):
+    """slices of the visible pages per (request, K/V head) for the tensor-core decode attention (two CTAs per SM). Cost model in
+    units of the memory latency: a CTA pays one latency to fill its copy ring and half of one per page after that (two pages in
+    flight); equal CTAs run in whole rounds of the resident ones."""
+    best, best_cost = 1, float('inf')
+    for ns in range(1, max(1, min(pages, 32)) + 1):
+        per = -(-pages // ns)
+        cost = -(-pairs * ns // slots) * (1.0 + per / 2.0)
+        if cost < best_cost - 1e-9:
+            best, best_cost = ns, cost
+    return best
+
+
 class StepBatch:
     """Device-side description of one engine step (built by engine.Engine.step)."""
     __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos', 'flat')
@@ -224,8 +237,7 @@ class TagenexB200:
                 w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
                 span = min(m.window, b.max_pos + 1) if m.window else b.max_pos + 1
                 if L['mma']:
-                    # tensor-core kernel: slices of whole pages, one wave of two CTAs per SM, a slice no shorter than a page
-                    w.n_splits = max(1, min(2 * 148 // (b.n_dec * G), 2 * -(-span // 128)))
+                    w.n_splits = _page_slices(b.n_dec * G, 2 * -(-span // 128) + 1)
                 else:
                     # one key per lane: enough CTAs for eight per SM, at least 128 keys (one pass of a CTA) per slice
                     w.n_splits = max(1, min(-(-8 * 148 // (b.n_dec * G)), -(-span // 128)))
