@@ -181,6 +181,33 @@ __global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT*
     }
 }
 
+// four columns per thread (F, both row pitches and the pointers are multiples of four elements): 16-byte loads
+template <typename AT>
+__global__ void glu_clamped_vec4_kernel(const float* __restrict__ gu, int64_t ld, AT* __restrict__ out, int64_t ldo, int64_t R, int F,
+                                        float limit, float alpha, const float* __restrict__ bias) {
+    const int F4 = F / 4;
+    const int64_t n = R * F4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F4; const int c = (int)(i % F4) * 4;
+        float4 g = *reinterpret_cast<const float4*>(gu + (size_t)r * ld + c);
+        float4 u = *reinterpret_cast<const float4*>(gu + (size_t)r * ld + F + c);
+        if (bias) {
+            const float4 bg = *reinterpret_cast<const float4*>(bias + c), bu = *reinterpret_cast<const float4*>(bias + F + c);
+            g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w; u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
+        }
+        float y[4];
+        const float gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float a = fminf(gg[k], limit), b = fminf(fmaxf(uu[k], -limit), limit);
+            y[k] = a * (1.0f / (1.0f + expf(-alpha * a))) * (b + 1.0f);
+        }
+        AT* o = out + (size_t)r * ldo + c;
+        if constexpr (sizeof(AT) == 4) *reinterpret_cast<float4*>(o) = make_float4(y[0], y[1], y[2], y[3]);
+        else *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+    }
+}
+
 // ---------------------------------------------------------------- router: fp32 logits, top-k (ties: lower index), softmax over the chosen
 // One CTA per token: the threads split the token's activations, eight experts per pass; partial sums are reduced in an order
 // fixed by the thread layout (lanes, then warps in ascending order), so a token's logits do not depend on the batch.
@@ -337,7 +364,8 @@ extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
     if (a->T == 0) return 0;
     P3_CHECK_ARG(a->dim <= 256 && a->vdim <= 256, "qkv_post: head sizes must be <= 256");
     const int jobs = a->n_heads + 2 * a->n_kv, th = 128;
-    // few tokens: one warp per job; many tokens: each CTA walks several jobs (the grid is large enough already)
+    // few tokens: one warp per job; many tokens: each CTA walks all jobs of its token (the grid is large enough already; spreading
+    // the jobs over more CTAs measured no faster)
     const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
     const dim3 grid((unsigned)a->T, (unsigned)groups);
     if (a->act_f32 && a->cache_f32) qk_norm_kv_write_kernel<float, float><<<grid, th, 0, st>>>(*a);
@@ -350,9 +378,14 @@ extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
 extern "C" int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, float limit, float alpha,
                               const float* bias, cudaStream_t st) {
     if (R == 0) return 0;
-    const int64_t n = R * F;
+    const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                     (!bias || ((uintptr_t)bias & 15) == 0);
+    const int64_t n = vec ? R * (F / 4) : R * F;
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
+    if (vec) {
+        if (out_f32) glu_clamped_vec4_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
+        else glu_clamped_vec4_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
+    } else if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
     else glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
     P3_CHECK_LAUNCH("glu_clamped");
     return 0;

@@ -161,10 +161,17 @@ class Engine:
             self._bind(sb, torch.empty_like(b.flat))
             sb.flat.copy_(b.flat)
             torch.cuda.synchronize()
-            ent['graph'] = torch.cuda.CUDAGraph()
-            with capture_graph(ent['graph']):
-                ent['out'] = self.model.forward(sb, self.pool)
-            ent['batch'] = sb
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with capture_graph(graph):
+                    out = self.model.forward(sb, self.pool)
+            except Exception:
+                # a step that cannot be captured runs eagerly, and so do all later ones (nothing of it has run yet)
+                self.use_graphs = False
+                self._graphs.clear()
+                torch.cuda.synchronize()
+                return self.model.forward(b, self.pool)
+            ent['graph'], ent['out'], ent['batch'] = graph, out, sb
         else:
             ent['batch'].flat.copy_(b.flat)
         ent['graph'].replay()
