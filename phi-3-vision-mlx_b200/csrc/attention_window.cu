@@ -28,6 +28,8 @@ constexpr int BQ = 32, WARPS = 4, RPW = BQ / WARPS;          // prefill: query r
 
 template <typename AT, typename CT, int DVC>
 __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn_window_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
     const int d = a.dim, dv = a.vdim, dp = (d + 3) & ~3;       // q rows padded to float4
     float* Qs = sm;                                          // [BQ][dp]
@@ -169,6 +171,8 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, i
 // diagonal, inside the window) skips the visibility tests.
 template <int DK, int DN>
 __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
     const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8;
@@ -350,6 +354,8 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f)
 // attn_window_merge_kernel combines them. The sink enters once, as the initial state of slice 0's first warp.
 template <typename AT, typename CT, int DVC>
 __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_window_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
     const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv, G = a.n_kv;
     float* Qs = sm;                                          // [RMAX][d]
@@ -509,6 +515,8 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 // (4-byte async copies into the stage), and the block-table entry of the page issued next is read one iteration ahead.
 template <int DK, int DN>
 __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_window_args a, int n_stages) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
     const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv;
@@ -690,6 +698,8 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
 // (base2: the slices' maxima are in the base-2 domain, as the tensor-core decode kernel keeps them)
 template <typename AT>
 __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, int base2) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     auto ex = [base2](float x) { return base2 ? exp2f(x) : expf(x); };
     const int t = blockIdx.x / a.n_heads, h = blockIdx.x % a.n_heads, dv = a.vdim;
     const int row = reinterpret_cast<const int4*>(a.tiles)[t].x;
@@ -738,7 +748,7 @@ int launch_prefill(const p3_attn_window_args* a, cudaStream_t st) {
     const int c = (a->vdim + 31) / 32;
 #define GO(N)                                                                                              \
     do { if (set_smem(attn_window_prefill_kernel<AT, CT, N>, bytes, "attn_window_prefill")) return -1;      \
-         attn_window_prefill_kernel<AT, CT, N><<<grid, WARPS * 32, bytes, st>>>(*a); } while (0)
+         p3_launch_pdl(attn_window_prefill_kernel<AT, CT, N>, dim3(grid), dim3(WARPS * 32), (size_t)(bytes), st, *a); } while (0)
     if (c <= 1) GO(1); else if (c <= 2) GO(2); else if (c <= 4) GO(4); else GO(8);
 #undef GO
     return 0;
@@ -752,10 +762,10 @@ int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
     const int cv = (a->vdim + 31) / 32;
 #define GO(NV)                                                                                             \
     do { if (set_smem(attn_window_decode_kernel<AT, CT, NV>, bytes, "attn_window_decode")) return -1;       \
-         attn_window_decode_kernel<AT, CT, NV><<<grid, DW * 32, bytes, st>>>(*a); } while (0)
+         p3_launch_pdl(attn_window_decode_kernel<AT, CT, NV>, dim3(grid), dim3(DW * 32), (size_t)(bytes), st, *a); } while (0)
     if (cv <= 1) GO(1); else if (cv <= 2) GO(2); else if (cv <= 4) GO(4); else GO(8);
 #undef GO
-    if (ns > 1) attn_window_merge_kernel<AT><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns, 0);
+    if (ns > 1) p3_launch_pdl(attn_window_merge_kernel<AT>, dim3((unsigned)(a->n_tiles * a->n_heads)), dim3(64), (size_t)(0), st, *a, ns, 0);
     return 0;
 }
 }  // namespace
@@ -773,10 +783,10 @@ static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
     const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads);
     if (a->dim <= 64 && a->vdim <= 64) {
         if (set_smem(attn_window_prefill_mma_kernel<4, 8>, bytes, "attn_window_prefill")) return -1;
-        attn_window_prefill_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a);
+        p3_launch_pdl(attn_window_prefill_mma_kernel<4, 8>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
     } else {
         if (set_smem(attn_window_prefill_mma_kernel<8, 16>, bytes, "attn_window_prefill")) return -1;
-        attn_window_prefill_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a);
+        p3_launch_pdl(attn_window_prefill_mma_kernel<8, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
     }
     return 0;
 }
@@ -792,12 +802,12 @@ static int launch_decode_mma(const p3_attn_window_args* a, cudaStream_t st) {
     const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
     if (a->dim <= 64 && a->vdim <= 64) {
         if (set_smem(attn_window_decode_mma_kernel<4, 8>, bytes, "attn_window_decode")) return -1;
-        attn_window_decode_mma_kernel<4, 8><<<grid, 128, bytes, st>>>(*a, nst);
+        p3_launch_pdl(attn_window_decode_mma_kernel<4, 8>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst);
     } else {
         if (set_smem(attn_window_decode_mma_kernel<8, 16>, bytes, "attn_window_decode")) return -1;
-        attn_window_decode_mma_kernel<8, 16><<<grid, 128, bytes, st>>>(*a, nst);
+        p3_launch_pdl(attn_window_decode_mma_kernel<8, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst);
     }
-    if (ns > 1) attn_window_merge_kernel<bf16><<<(unsigned)(a->n_tiles * a->n_heads), 64, 0, st>>>(*a, ns, 1);
+    if (ns > 1) p3_launch_pdl(attn_window_merge_kernel<bf16>, dim3((unsigned)(a->n_tiles * a->n_heads)), dim3(64), (size_t)(0), st, *a, ns, 1);
     return 0;
 }
 

@@ -44,6 +44,8 @@ __device__ __forceinline__ bool find_tile(const AnyP& p, int tile, int& g, int64
 
 template <typename XT, typename WT, typename OT>
 __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Bs[BK][BN + 4];
     int g; int64_t m0, m1;
@@ -98,6 +100,8 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
 constexpr int TK = 32;                                     // k elements per stage
 template <typename OT>
 __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     __shared__ __align__(16) bf16 As[BM][TK + 8];
     __shared__ __align__(16) bf16 Bs[BN][TK + 8];
     int g; int64_t m0, m1;
@@ -189,17 +193,17 @@ extern "C" int p3_gemm_any(const p3_gemm_any_args* a, cudaStream_t st) {
     const unsigned mt = (unsigned)((a->M + BM - 1) / BM) + (a->seg_offsets ? (unsigned)a->n_groups : 0u);
     const dim3 grid(mt, (unsigned)((a->N + BN - 1) / BN));
     if (a->x_f32) {
-        if (a->out_f32) gemm_any_fma_kernel<float, float, float><<<grid, 256, 0, st>>>(p);
-        else gemm_any_fma_kernel<float, float, bf16><<<grid, 256, 0, st>>>(p);
+        if (a->out_f32) p3_launch_pdl(gemm_any_fma_kernel<float, float, float>, dim3(grid), dim3(256), (size_t)(0), st, p);
+        else p3_launch_pdl(gemm_any_fma_kernel<float, float, bf16>, dim3(grid), dim3(256), (size_t)(0), st, p);
     } else {
         const bool tc = a->K % 8 == 0 && a->ldx % 8 == 0 && a->ldw % 8 == 0 && a->w_group_stride % 8 == 0 &&
                         ((uintptr_t)a->X & 15) == 0 && ((uintptr_t)a->W & 15) == 0 && !a->force_fma;
         if (tc) {
-            if (a->out_f32) gemm_any_mma_kernel<float><<<grid, 128, 0, st>>>(p);
-            else gemm_any_mma_kernel<bf16><<<grid, 128, 0, st>>>(p);
+            if (a->out_f32) p3_launch_pdl(gemm_any_mma_kernel<float>, dim3(grid), dim3(128), (size_t)(0), st, p);
+            else p3_launch_pdl(gemm_any_mma_kernel<bf16>, dim3(grid), dim3(128), (size_t)(0), st, p);
         } else {
-            if (a->out_f32) gemm_any_fma_kernel<bf16, bf16, float><<<grid, 256, 0, st>>>(p);
-            else gemm_any_fma_kernel<bf16, bf16, bf16><<<grid, 256, 0, st>>>(p);
+            if (a->out_f32) p3_launch_pdl(gemm_any_fma_kernel<bf16, bf16, float>, dim3(grid), dim3(256), (size_t)(0), st, p);
+            else p3_launch_pdl(gemm_any_fma_kernel<bf16, bf16, bf16>, dim3(grid), dim3(256), (size_t)(0), st, p);
         }
     }
     P3_CHECK_LAUNCH("gemm_any");

@@ -36,6 +36,8 @@ constexpr int RPT = 8;
 template <typename AT>
 __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ x,
                                   AT* __restrict__ xa, int W, int vocab) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int64_t t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;
@@ -56,6 +58,8 @@ __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t*
 template <typename AT>
 __global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ ybias,
                                          const float* __restrict__ gain, float* x, AT* __restrict__ xa, int W, float eps) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     __shared__ float sh[32];
     const int64_t t = blockIdx.x;
     const float* yr = y + (size_t)t * ldy;
@@ -89,6 +93,8 @@ __global__ void postnorm_residual_kernel(const float* __restrict__ y, int64_t ld
 template <typename AT>
 __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ gain,
                                     AT* __restrict__ out, int W, float eps) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     __shared__ float sh[32];
     const int64_t r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * W;
@@ -112,6 +118,8 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const int32_t* 
 // logits into gates. A head's numbers stay in registers between the statistic and the write (head sizes <= 256: 8 per lane).
 template <typename AT, typename CT>
 __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const float* pr = a.proj + (size_t)t * a.ld_proj;
     const int slot = a.tok_slot[t], pos = a.tok_pos[t];
@@ -172,6 +180,8 @@ __global__ void qk_norm_kv_write_kernel(p3_qkv_post_args a) {
 template <typename AT>
 __global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT* __restrict__ out, int64_t ldo, int64_t R, int F,
                                    float limit, float alpha, const float* __restrict__ bias) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int64_t n = R * F;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / F; const int c = (int)(i % F);
@@ -185,6 +195,8 @@ __global__ void glu_clamped_kernel(const float* __restrict__ gu, int64_t ld, AT*
 template <typename AT>
 __global__ void glu_clamped_vec4_kernel(const float* __restrict__ gu, int64_t ld, AT* __restrict__ out, int64_t ldo, int64_t R, int F,
                                         float limit, float alpha, const float* __restrict__ bias) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int F4 = F / 4;
     const int64_t n = R * F4;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -214,6 +226,8 @@ __global__ void glu_clamped_vec4_kernel(const float* __restrict__ gu, int64_t ld
 template <typename AT>
 __global__ void router_topk_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr, const float* __restrict__ br,
                                    int T, int W, int E, int top, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ float z[];                             // [E] logits, then [warps][8] partial sums
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -268,6 +282,8 @@ __global__ void router_topk_kernel(const AT* __restrict__ x, int64_t ldx, const 
 // choice of sorted row r; where[token * top + choice] = r.
 __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n, int E, int32_t* __restrict__ seg,
                                 int32_t* __restrict__ order, int32_t* __restrict__ where) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     __shared__ int sh_w[33];
     __shared__ int sh_base;
     const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -300,6 +316,8 @@ __global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int n, int E, i
 template <typename AT>
 __global__ void gather_rows_kernel(const AT* __restrict__ x, int64_t ldx, const int32_t* __restrict__ rows, int div,
                                    AT* __restrict__ out, int W) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int64_t r = blockIdx.x;
     const AT* src = x + (size_t)(rows[r] / div) * ldx;
     for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)r * W + i] = src[i];
@@ -308,6 +326,8 @@ __global__ void gather_rows_kernel(const AT* __restrict__ x, int64_t ldx, const 
 // ---------------------------------------------------------------- out[t] = sum_j w[t][j] * y[where[t * top + j]]   (j ascending)
 __global__ void moe_combine_kernel(const float* __restrict__ y, int64_t ldy, const int32_t* __restrict__ where,
                                    const float* __restrict__ wts, int top, float* __restrict__ out, int W) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ float cw[];                            // [top] weights, then [top] sorted rows
     int* rows = reinterpret_cast<int*>(cw + top);
     const int64_t t = blockIdx.x;
@@ -323,6 +343,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int64_t ldy, con
 
 // ---------------------------------------------------------------- pen[h][dist] = r1_h * ln(1 + r2_h * dist)
 __global__ void distance_penalty_kernel(const float* __restrict__ r1, const float* __restrict__ r2, float* __restrict__ pen, int H, int n) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int h = blockIdx.y;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         pen[(size_t)h * n + i] = r1[h] * log1pf(r2[h] * (float)i);
@@ -332,8 +354,8 @@ __global__ void distance_penalty_kernel(const float* __restrict__ r1, const floa
 extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
                                  cudaStream_t st) {
     if (T == 0) return 0;
-    if (act_f32) embed_rows_kernel<float><<<(unsigned)T, 128, 0, st>>>((const bf16*)table, ids, x, (float*)x_act, W, vocab);
-    else embed_rows_kernel<bf16><<<(unsigned)T, 128, 0, st>>>((const bf16*)table, ids, x, (bf16*)x_act, W, vocab);
+    if (act_f32) p3_launch_pdl(embed_rows_kernel<float>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (float*)x_act, W, vocab);
+    else p3_launch_pdl(embed_rows_kernel<bf16>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (bf16*)x_act, W, vocab);
     P3_CHECK_LAUNCH("embed_rows_f32");
     return 0;
 }
@@ -342,8 +364,8 @@ extern "C" int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_
                                     int64_t T, int W, float eps, cudaStream_t st) {
     if (T == 0) return 0;
     const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;     // the row fits the threads' registers up to W = 8192
-    if (act_f32) postnorm_residual_kernel<float><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (float*)x_act, W, eps);
-    else postnorm_residual_kernel<bf16><<<(unsigned)T, th, 0, st>>>(y, ldy, y_bias, gain, x, (bf16*)x_act, W, eps);
+    if (act_f32) p3_launch_pdl(postnorm_residual_kernel<float>, dim3((unsigned)T), dim3(th), (size_t)(0), st, y, ldy, y_bias, gain, x, (float*)x_act, W, eps);
+    else p3_launch_pdl(postnorm_residual_kernel<bf16>, dim3((unsigned)T), dim3(th), (size_t)(0), st, y, ldy, y_bias, gain, x, (bf16*)x_act, W, eps);
     P3_CHECK_LAUNCH("postnorm_residual");
     return 0;
 }
@@ -352,8 +374,8 @@ extern "C" int p3_rmsnorm_rows_f32(const float* x, const int32_t* rows, const fl
                                    float eps, cudaStream_t st) {
     if (R == 0) return 0;
     const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;
-    if (out_f32) rmsnorm_rows_kernel<float><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (float*)out, W, eps);
-    else rmsnorm_rows_kernel<bf16><<<(unsigned)R, th, 0, st>>>(x, rows, gain, (bf16*)out, W, eps);
+    if (out_f32) p3_launch_pdl(rmsnorm_rows_kernel<float>, dim3((unsigned)R), dim3(th), (size_t)(0), st, x, rows, gain, (float*)out, W, eps);
+    else p3_launch_pdl(rmsnorm_rows_kernel<bf16>, dim3((unsigned)R), dim3(th), (size_t)(0), st, x, rows, gain, (bf16*)out, W, eps);
     P3_CHECK_LAUNCH("rmsnorm_rows_f32");
     return 0;
 }
@@ -368,8 +390,8 @@ extern "C" int p3_qkv_post(const p3_qkv_post_args* a, cudaStream_t st) {
     // the jobs over more CTAs measured no faster)
     const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
     const dim3 grid((unsigned)a->T, (unsigned)groups);
-    if (a->act_f32 && a->cache_f32) qk_norm_kv_write_kernel<float, float><<<grid, th, 0, st>>>(*a);
-    else if (!a->act_f32 && !a->cache_f32) qk_norm_kv_write_kernel<bf16, bf16><<<grid, th, 0, st>>>(*a);
+    if (a->act_f32 && a->cache_f32) p3_launch_pdl(qk_norm_kv_write_kernel<float, float>, dim3(grid), dim3(th), (size_t)(0), st, *a);
+    else if (!a->act_f32 && !a->cache_f32) p3_launch_pdl(qk_norm_kv_write_kernel<bf16, bf16>, dim3(grid), dim3(th), (size_t)(0), st, *a);
     else P3_CHECK_ARG(false, "qkv_post: activations and cache must both be fp32 or both bf16");
     P3_CHECK_LAUNCH("qkv_post");
     return 0;
@@ -383,10 +405,10 @@ extern "C" int p3_glu_clamped(const float* gu, int64_t ld, void* out, int64_t ld
     const int64_t n = vec ? R * (F / 4) : R * F;
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     if (vec) {
-        if (out_f32) glu_clamped_vec4_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
-        else glu_clamped_vec4_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
-    } else if (out_f32) glu_clamped_kernel<float><<<grid, 256, 0, st>>>(gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
-    else glu_clamped_kernel<bf16><<<grid, 256, 0, st>>>(gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
+        if (out_f32) p3_launch_pdl(glu_clamped_vec4_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
+        else p3_launch_pdl(glu_clamped_vec4_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
+    } else if (out_f32) p3_launch_pdl(glu_clamped_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, gu, ld, (float*)out, ldo, R, F, limit, alpha, bias);
+    else p3_launch_pdl(glu_clamped_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, gu, ld, (bf16*)out, ldo, R, F, limit, alpha, bias);
     P3_CHECK_LAUNCH("glu_clamped");
     return 0;
 }
@@ -397,15 +419,15 @@ extern "C" int p3_router_topk(const void* x, int64_t ldx, int x_f32, const float
     if (T == 0) return 0;
     const int nw = W >= 1024 ? 8 : 4;
     const size_t sm = ((size_t)E + nw * 8) * sizeof(float);
-    if (x_f32) router_topk_kernel<float><<<(unsigned)T, nw * 32, sm, st>>>((const float*)x, ldx, Wr, br, T, W, E, top, ids, wts);
-    else router_topk_kernel<bf16><<<(unsigned)T, nw * 32, sm, st>>>((const bf16*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    if (x_f32) p3_launch_pdl(router_topk_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, br, T, W, E, top, ids, wts);
+    else p3_launch_pdl(router_topk_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, br, T, W, E, top, ids, wts);
     P3_CHECK_LAUNCH("router_topk");
     return 0;
 }
 
 extern "C" int p3_moe_sort(const int32_t* ids, int n, int E, int32_t* seg, int32_t* order, int32_t* where, cudaStream_t st) {
     P3_CHECK_ARG(n >= 1 && E >= 1, "moe_sort: empty");
-    moe_sort_kernel<<<E, 1024, 0, st>>>(ids, n, E, seg, order, where);
+    p3_launch_pdl(moe_sort_kernel, dim3(E), dim3(1024), (size_t)(0), st, ids, n, E, seg, order, where);
     P3_CHECK_LAUNCH("moe_sort");
     return 0;
 }
@@ -414,8 +436,8 @@ extern "C" int p3_gather_rows(const void* x, int64_t ldx, int x_f32, const int32
                               cudaStream_t st) {
     P3_CHECK_ARG(div >= 1 && rows, "gather_rows: need an index list and div >= 1");
     if (R == 0) return 0;
-    if (x_f32) gather_rows_kernel<float><<<(unsigned)R, 128, 0, st>>>((const float*)x, ldx, rows, div, (float*)out, W);
-    else gather_rows_kernel<bf16><<<(unsigned)R, 128, 0, st>>>((const bf16*)x, ldx, rows, div, (bf16*)out, W);
+    if (x_f32) p3_launch_pdl(gather_rows_kernel<float>, dim3((unsigned)R), dim3(128), (size_t)(0), st, (const float*)x, ldx, rows, div, (float*)out, W);
+    else p3_launch_pdl(gather_rows_kernel<bf16>, dim3((unsigned)R), dim3(128), (size_t)(0), st, (const bf16*)x, ldx, rows, div, (bf16*)out, W);
     P3_CHECK_LAUNCH("gather_rows");
     return 0;
 }
@@ -423,14 +445,14 @@ extern "C" int p3_gather_rows(const void* x, int64_t ldx, int x_f32, const int32
 extern "C" int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const float* wts, int top, float* out, int64_t T, int W,
                               cudaStream_t st) {
     if (T == 0) return 0;
-    moe_combine_kernel<<<(unsigned)T, W >= 1024 ? 256 : 128, (size_t)top * 8, st>>>(y, ldy, where, wts, top, out, W);
+    p3_launch_pdl(moe_combine_kernel, dim3((unsigned)T), dim3(W >= 1024 ? 256 : 128), (size_t)((size_t)top * 8), st, y, ldy, where, wts, top, out, W);
     P3_CHECK_LAUNCH("moe_combine");
     return 0;
 }
 
 extern "C" int p3_distance_penalty_table(const float* r1, const float* r2, float* pen, int H, int n, cudaStream_t st) {
     P3_CHECK_ARG(H >= 1 && n >= 1, "distance_penalty_table: empty");
-    distance_penalty_kernel<<<dim3((unsigned)((n + 255) / 256), (unsigned)H), 256, 0, st>>>(r1, r2, pen, H, n);
+    p3_launch_pdl(distance_penalty_kernel, dim3(dim3((unsigned)((n + 255) / 256), (unsigned)H)), dim3(256), (size_t)(0), st, r1, r2, pen, H, n);
     P3_CHECK_LAUNCH("distance_penalty_table");
     return 0;
 }
