@@ -255,13 +255,20 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
         float mx0 = -FLT_MAX, mx1 = -FLT_MAX;
         // every key of the page is visible to every row of the tile: behind the first row, and the last row's window reaches it
         const bool full = pg * P3_PAGE + 63 <= pos0 && (a.window <= 0 || pos0 + 63 - pg * P3_PAGE < a.window);
+        // the penalty depends on row - col only, and this thread's second row is its first plus 8: the penalties of (r1, key block
+        // j) are those of (r0, key block j - 1), so 18 values serve the 32 scores
+        float pq[9][2];
+#pragma unroll
+        for (int j = 0; j < 9; j++) {
+            pq[j][0] = ps[r0 - ((j - 1) * 8 + tig * 2) + 63];
+            pq[j][1] = ps[r0 - ((j - 1) * 8 + tig * 2 + 1) + 63];
+        }
         if (full) {
 #pragma unroll
             for (int j = 0; j < 8; j++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
-                    const float v = fmaf(s[j][e], scale2, -ps[row - col + 63]);
+                    const float v = fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]);
                     s[j][e] = v;
                     if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
                 }
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
                     const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
                     const int dist = pos0 + row - (pg * P3_PAGE + col);
                     const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
-                    const float v = vis ? fmaf(s[j][e], scale2, -ps[row - col + 63]) : -FLT_MAX;
+                    const float v = vis ? fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]) : -FLT_MAX;
                     s[j][e] = v;
                     if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
                 }
@@ -294,8 +301,10 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
                 if (e < 2) ps0 += p; else ps1 += p;
             }
         l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {   // a maximum moved somewhere in the warp (a factor of exactly 1 changes nothing)
 #pragma unroll
-        for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+        }
 #pragma unroll
         for (int t = 0; t < 4; t++) {                        // 16 keys per step
             uint32_t pa[4];
@@ -636,8 +645,10 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
                     if (e < 2) ps0 += p; else ps1 += p;
                 }
             l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+            if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
 #pragma unroll
-            for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+                for (int n = 0; n < DN; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+            }
             uint32_t pa[4];
             pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
             pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
