@@ -96,8 +96,10 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
 
 // bf16 x bf16 on the tensor cores: 64 x 64 tile, 4 warps (2 x 2), each warp 32 x 32 = 2 x 4 MMAs of m16n8k16 per 16-wide k
 // step; operands staged through shared memory as bf16 (row-major [row][k], 16-byte chunks, K % 8 == 0 and 16-byte aligned rows
-// required by the launcher). Same tile walk, gather and segment logic as the FMA kernel.
-constexpr int TK = 32;                                     // k elements per stage
+// required by the launcher). Same tile walk, gather and segment logic as the FMA kernel. A k-slab is 128 elements: 16 lanes read
+// the 256 contiguous bytes of one row, so that with few rows, where the kernel is a stream of W, DRAM sees bursts instead of
+// 64-byte pieces of 64 rows; the next slab's loads are in flight while this one is multiplied.
+constexpr int TK = 128;                                    // k elements per stage
 template <typename OT>
 __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
@@ -110,35 +112,33 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
     const bf16* X = (const bf16*)p.X;
     const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride;
-    // staging: 64 rows x 4 chunks of 8 elements = 256 chunks per operand, 2 per thread
-    const bf16* arow[2]; const bf16* brow[2]; int srow[2], schunk[2];
+    // staging: 64 rows x 16 chunks of 8 elements per operand; round j: row 8 j + 2 warp + lane / 16, chunk lane % 16
+    const int srow0 = 2 * warp + (lane >> 4), schunk = (lane & 15) * 8;
+    int64_t aoff[8];                                        // element offset of this thread's A row in round j, -1: no such row
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int c = tid + j * 128;
-        srow[j] = c >> 2; schunk[j] = (c & 3) * 8;
-        const int64_t am = m0 + srow[j];
-        arow[j] = (am < m1) ? X + (size_t)(p.x_rows ? p.x_rows[am] / p.x_row_div : am) * p.ldx : nullptr;
-        brow[j] = (n0 + srow[j] < p.N) ? W + (size_t)(n0 + srow[j]) * p.ldw : nullptr;
+    for (int j = 0; j < 8; j++) {
+        const int64_t am = m0 + srow0 + 8 * j;
+        aoff[j] = (am < m1) ? (int64_t)(p.x_rows ? p.x_rows[am] / p.x_row_div : am) * p.ldx : -1;
     }
+    const bf16* brow0 = W + (size_t)(n0 + srow0) * p.ldw;
     float acc[2][4][4] = {};
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    // register double buffering: the next k-slab's global loads are in flight while this one is multiplied
-    uint4 ra[2], rb[2];
+    uint4 ra[8], rb[8];
     auto fetch = [&](int k0) {
+        const int k = k0 + schunk;
+        const bool in = k < p.K;                           // K % 8 == 0: a chunk is inside or outside as a whole
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int k = k0 + schunk[j];
-            const bool in = k < p.K;                       // K % 8 == 0: a chunk is inside or outside as a whole
-            ra[j] = (arow[j] && in) ? __ldg(reinterpret_cast<const uint4*>(arow[j] + k)) : zero;
-            rb[j] = (brow[j] && in) ? ldg_nc_v4(brow[j] + k) : zero;
+        for (int j = 0; j < 8; j++) {
+            ra[j] = (aoff[j] >= 0 && in) ? __ldg(reinterpret_cast<const uint4*>(X + aoff[j] + k)) : zero;
+            rb[j] = (n0 + srow0 + 8 * j < p.N && in) ? ldg_nc_v4(brow0 + (size_t)(8 * j) * p.ldw + k) : zero;
         }
     };
     fetch(0);
     for (int k0 = 0; k0 < p.K; k0 += TK) {
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            *reinterpret_cast<uint4*>(&As[srow[j]][schunk[j]]) = ra[j];
-            *reinterpret_cast<uint4*>(&Bs[srow[j]][schunk[j]]) = rb[j];
+        for (int j = 0; j < 8; j++) {
+            *reinterpret_cast<uint4*>(&As[srow0 + 8 * j][schunk]) = ra[j];
+            *reinterpret_cast<uint4*>(&Bs[srow0 + 8 * j][schunk]) = rb[j];
         }
         __syncthreads();
         if (k0 + TK < p.K) fetch(k0 + TK);

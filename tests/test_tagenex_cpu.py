@@ -147,3 +147,14 @@ def test_oracle_mechanisms():
     w = {'r.router': torch.eye(3), 'r.router.b': torch.tensor([0.0, 0.0, 5.0])}
     idx, wt = O.route(torch.tensor([[1.0, 2.0, -9.0]]), w, 'r.', 2)
     assert idx.tolist() == [[1, 0]] and torch.allclose(wt, torch.softmax(torch.tensor([[2.0, 1.0]]), -1))
+
+
+def test_decode_attention_slices_fill_the_gpu_without_splitting_pages():
+    from phi3_b200.tagenex import _page_slices
+    for pairs in (1, 2, 7, 32, 64, 128, 300, 512, 4096):
+        for pages in (1, 2, 3, 17, 40):
+            ns = _page_slices(pairs, pages)
+            assert 1 <= ns <= pages
+    assert _page_slices(1, 17) == 17                         # one request, one K/V head: a page per CTA
+    assert _page_slices(4096, 17) == 1                       # more pairs than resident CTAs: whole contexts
+    assert _page_slices(128, 17) * 128 <= 2 * 148            # a single round when one fits
