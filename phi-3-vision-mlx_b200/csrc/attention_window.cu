@@ -149,6 +149,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     }
 }
 
+// 2^x on the special-function unit (one instruction; -FLT_MAX and -inf give 0)
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // 64 rows of a page (row-major, `chunks` 16-byte pieces per row) -> shared memory rows of pitch ld, by 128 threads: LPR lanes per
 // row (chunks <= LPR), no division in the address arithmetic
 template <int LPR>
@@ -268,9 +275,7 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
             for (int j = 0; j < 8; j++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const float v = fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]);
-                    s[j][e] = v;
-                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                    s[j][e] = fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]);
                 }
         } else {
 #pragma unroll
@@ -280,26 +285,35 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
                     const int row = (e < 2) ? r0 : r1, col = j * 8 + tig * 2 + (e & 1);
                     const int dist = pos0 + row - (pg * P3_PAGE + col);
                     const bool vis = row < nq && dist >= 0 && (a.window <= 0 || dist < a.window);
-                    const float v = vis ? fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]) : -FLT_MAX;
-                    s[j][e] = v;
-                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                    s[j][e] = vis ? fmaf(s[j][e], scale2, -pq[(e < 2) ? j + 1 : j][e & 1]) : -FLT_MAX;
                 }
+        }
+        {   // row maxima by a tree (depth 4 instead of a chain of 16)
+            float t0[8], t1[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) { t0[j] = fmaxf(s[j][0], s[j][1]); t1[j] = fmaxf(s[j][2], s[j][3]); }
+#pragma unroll
+            for (int w = 4; w > 0; w >>= 1)
+#pragma unroll
+                for (int j = 0; j < w; j++) { t0[j] = fmaxf(t0[j], t0[j + w]); t1[j] = fmaxf(t1[j], t1[j + w]); }
+            mx0 = t0[0]; mx1 = t1[0];
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);   // m is finite (sink) or -FLT_MAX: the difference is finite or -inf
+        const float c0 = ex2f(m0 - n0), c1 = ex2f(m1 - n1);     // m is finite (sink) or -FLT_MAX: the difference is finite or -inf
         m0 = n0; m1 = n1;
-        float ps0 = 0.f, ps1 = 0.f;
+        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f};   // four partial row sums each: short dependency chains
 #pragma unroll
         for (int j = 0; j < 8; j++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const float v = s[j][e];
-                const float p = (full || v > -FLT_MAX) ? exp2f(v - ((e < 2) ? n0 : n1)) : 0.f;
+                const float p = (full || v > -FLT_MAX) ? ex2f(v - ((e < 2) ? n0 : n1)) : 0.f;
                 s[j][e] = p;
-                if (e < 2) ps0 += p; else ps1 += p;
+                if (e < 2) q0[(j & 1) * 2 + e] += p; else q1[(j & 1) * 2 + (e & 1)] += p;
             }
+        const float ps0 = (q0[0] + q0[1]) + (q0[2] + q0[3]), ps1 = (q1[0] + q1[1]) + (q1[2] + q1[3]);
         l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
         if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {   // a maximum moved somewhere in the warp (a factor of exactly 1 changes nothing)
 #pragma unroll
