@@ -305,6 +305,78 @@ def test_small_batches_take_the_weight_streaming_products(lib):
     assert_close(run_schedule(model, toks, [20]), dec, B16)
 
 
+def _random_config(rng):
+    """a configuration drawn at random: layer count and order, head counts, group sizes, key / value sizes (with and without the
+    tensor-core kernels), windows from 1 to beyond the context, layers with and without value mixing, dense / mixture / no
+    feed-forward, top from 1 to all experts"""
+    width, vocab = rng.choice([64, 96, 128, 160, 200, 256]), rng.choice([97, 256, 1000])
+    gv, vd = rng.choice([1, 2, 4]), rng.choice([16, 24, 40, 64])             # value shape shared by the mixing layers
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        mix = rng.random() < 0.7
+        kv = gv if mix else rng.choice([1, 2, 3])
+        dim = rng.choice([16, 24, 48, 80, 128])
+        m = dict(heads=kv * rng.choice([1, 2, 5, 8]), kv_heads=kv, dim=dim, vdim=vd if mix else rng.choice([8, 20, 48, 128]),
+                 scale=rng.choice([dim ** -0.5, 0.05]), v_mix=mix)
+        win = rng.choice([0, 1, 7, 33, 64, 100, 129, 300])
+        if win:
+            m['mask'] = {'size': win}
+        k = rng.random()
+        if k < 0.15:
+            mlp = None
+        elif k < 0.55:
+            mlp = {'kind': 'dense', 'ff': rng.choice([64, 100, 136]), 'limit': rng.choice([1.0, 7.0])}
+        else:
+            e = rng.choice([1, 2, 6, 16])
+            mlp = {'kind': 'moe', 'expert': {'ff': rng.choice([32, 56]), 'limit': 3.0}, 'router': {'experts': e, 'top': rng.randint(1, e)}}
+        layers.append({'type': 'attention', 'mixer': m, 'mlp': mlp})
+    return {'architecture': 'Tagenex', 'vocab': vocab, 'width': width, 'norm': {'eps': rng.choice([1e-5, 1e-6])}, 'layers': layers}
+
+
+@pytest.mark.parametrize('seed', [11, 12, 13, 14])
+def test_random_configurations_under_random_schedules(lib, seed):
+    """five requests of unequal length through a four-slot engine whose pool holds less than their sum: random portions (down to
+    one token) beside decoded tokens, requests that sit out steps, slots and pages taken over by later requests"""
+    import random
+    configs, weights, engine, tagenex, paged, O = _mods()
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    w = weights.random_tagenex_weights(cfg, seed)
+    lens = {'a': rng.randint(130, 330), 'b': rng.randint(2, 90), 'c': rng.randint(60, 200), 'd': rng.randint(1, 40), 'e': rng.randint(65, 130)}
+    toks = {k: tokens(n, cfg['vocab'], 100 * seed + i) for i, (k, n) in enumerate(lens.items())}
+    ref = {k: O.forward(cfg, w, t, torch.float64) for k, t in toks.items()}
+    for dtype in (F32, B16):
+        model = tagenex.TagenexB200(cfg, w, dtype=dtype)
+        eng = engine.Engine(model, 64 * 12, 4)
+        for p in eng.pool.k + eng.pool.v:
+            p.fill_(9.0)
+        at, got = {k: 0 for k in toks}, {k: [] for k in toks}
+        waiting, live, srng = list(toks), [], random.Random(seed)
+        while waiting or live:
+            while waiting and len(live) < 4 and sum(-(-lens[k] // 64) for k in live + waiting[:1]) <= eng.pool.n_pages:
+                live.append(waiting.pop(0))
+            entries, end = [], []
+            for k in live:
+                if srng.random() < 0.15 and len(live) > 1:
+                    continue
+                n = 1 if at[k] > 0.6 * lens[k] else min(lens[k] - at[k], srng.choice([1, 1, 2, 3, 17, 64, 65, 130]))
+                entries.append((k, toks[k][at[k]:at[k] + n], list(range(n))))
+                at[k] += n
+                if at[k] == lens[k]:
+                    end.append(k)
+            if not entries:
+                continue
+            lg = eng.step(entries, end)
+            o = 0
+            for k, t, wnt in entries:
+                got[k].append(lg[o:o + len(wnt)])
+                o += len(wnt)
+            live = [k for k in live if k not in end]
+        for k in toks:
+            assert_close(torch.cat(got[k], 0), ref[k], dtype, (seed, k, cfg))
+        assert len(eng.pool.free_pages) == eng.pool.n_pages and len(eng.pool.free_slots) == 4
+
+
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 def _attention_case(lib, dtype, H, G, d, dv, window, n_ctx, hot, scale=1.0, seed=0, tile_rows=32, n_splits=1):
     """random q/k/v with a few dominant (query, key) pairs `hot` = [(i, j)]: both rows get a large common component so that
