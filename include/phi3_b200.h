@@ -320,7 +320,10 @@ int p3_decode_mega(const p3_mega_args* args, cudaStream_t st);
  * (mma.sync when K, ldx, ldw are multiples of 8 and the bases 16-byte aligned, else FMA); fp32 accumulation in ascending k.
  * x_rows (may be NULL): row r reads X[x_rows[r] / x_row_div]. seg_offsets (device int32 [n_groups + 1], may be NULL): rows
  * [seg[g], seg[g+1]) multiply with W + g * w_group_stride and add bias + g * bias_group_stride (grouped expert product; M is
- * then the total row count = seg[n_groups]). bias fp32 or NULL. */
+ * then the total row count = seg[n_groups]). bias fp32 or NULL.
+ * n_batch > 1: that many independent products in one launch (per-head products of an attention mixer); product b reads X, W and
+ * writes out at the element offsets b * x_batch_stride, b * w_batch_stride, b * out_batch_stride (column blocks of wider
+ * matrices). gate (fp32 logits [M, ld_gate], may be NULL): out <- out * sigmoid(gate[m][b * out_batch_stride + n]). */
 typedef struct {
     const void* X; int64_t ldx; int32_t x_f32; const int32_t* x_rows; int32_t x_row_div;
     const void* W; int64_t ldw; int32_t w_f32; int64_t w_group_stride;
@@ -329,12 +332,15 @@ typedef struct {
     int64_t M; int32_t N, K;
     const int32_t* seg_offsets; int32_t n_groups;
     int32_t force_fma;           /* tests: bf16 operands on the FMA kernel */
+    int32_t n_batch; int64_t x_batch_stride, w_batch_stride, out_batch_stride;
+    const float* gate; int64_t ld_gate;
 } p3_gemm_any_args;
 int p3_gemm_any(const p3_gemm_any_args* args, cudaStream_t st);
 
-/* x fp32 [T,W] = table[ids] (bf16 table); x_act (may be NULL) receives the same rows in the activation type */
+/* x fp32 [T,W] = table[ids] * scale (bf16 table); x_act (may be NULL; row pitch ld_act) receives the same rows in the activation
+ * type */
 int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
-                      cudaStream_t st);
+                      float scale, int64_t ld_act, cudaStream_t st);
 /* norm on a sublayer's OUTPUT: y' = y + y_bias (y_bias fp32 [W] or NULL: a bias the producing product left out);
  * x += y' / sqrt(mean(y'^2) + eps) * gain; x_act (may be NULL) = the new x in the activation type */
 int p3_postnorm_residual(const float* y, int64_t ldy, const float* y_bias, const float* gain, float* x, void* x_act, int act_f32,
@@ -373,6 +379,9 @@ typedef struct {
     const int32_t* tiles; int32_t n_tiles;
     int32_t n_splits; float* ws;   /* decode only: key slices per request (<= 1: none) and their workspace, fp32
                                       [n_tiles][n_heads][n_splits][vdim + 2] */
+    int32_t v_ld;                  /* elements between the value rows of a page (0: vdim). With v_pool == k_pool and v_ld == dim
+                                      the values are the leading vdim numbers of the key rows (one latent vector per token that
+                                      serves as key and as value) */
 } p3_attn_window_args;
 /* query rows per tile that p3_attn_window_prefill takes for these sizes: 64 on its tensor-core path, else 32 */
 int p3_attn_window_tile_rows(const p3_attn_window_args* args);
@@ -395,6 +404,50 @@ int p3_moe_combine(const float* y, int64_t ldy, const int32_t* where, const floa
                    cudaStream_t st);
 /* pen[h][i] = r1[h] * ln(1 + r2[h] * i), i < n */
 int p3_distance_penalty_table(const float* r1, const float* r2, float* pen, int H, int n, cudaStream_t st);
+
+
+/* ---- parts of decoders whose layers read ONE layer norm (weight and bias) and add all sublayer outputs at once, with a
+ * latent-vector attention cache and sigmoid-scored, group-limited expert routing (Tapalix and designs built from these parts) */
+
+/* v = x[t] + add1[t] + add2[t] (each may be NULL), t = rows ? rows[r] : r. Without `rows` and with an addend x[t] <- v.
+ * x_act (may be NULL, pitch ld_xact): v in the activation type; h_out (may be NULL, pitch ld_h): (v - mean) / sqrt(var + eps)
+ * * gain + bias in the activation type. Sums, mean and variance are fp32. */
+int p3_residual_layernorm(float* x, const float* add1, int64_t ld1, const float* add2, int64_t ld2, const int32_t* rows,
+                          const float* gain, const float* bias, void* x_act, int64_t ld_xact, void* h_out, int64_t ld_h,
+                          int act_f32, int64_t R, int W, float eps, cudaStream_t st);
+
+/* After the fused input projection of a latent-attention mixer (proj fp32 [T, ld_proj]):
+ *   q at q_off: n_heads x (dim plain | rot_dim turning). Plain parts -> q_plain (act) [T, ld_qp], head h at column h * dim;
+ *     turning parts are rotated and go to q_lat (act) [T, ld_ql] at column h * (kv_rank + rot_dim) + kv_rank (the leading kv_rank
+ *     columns of every head are filled later by the product with the key up-projection).
+ *   latent at c_off: kv_rank numbers, RMS-normed with c_gain -> cache row columns [0, kv_rank); the rot_dim numbers behind them
+ *     are rotated (not normed) -> cache row columns [kv_rank, kv_rank + rot_dim). cache: [page][64][kv_rank + rot_dim].
+ *   rotation: the first rot_n numbers of a turning part, element i paired with i + rot_n / 2, angle = position * freq[i]
+ *     (freq fp32 [rot_n / 2]), cos and sin times rot_mag; the rest passes unchanged.
+ *   gated unit (n_ff > 0): hid (act) [T, ld_hid] columns [hid_off, hid_off + n_ff) = silu(proj[gate_off + i]) * proj[up_off + i]. */
+typedef struct {
+    const float* proj; int64_t ld_proj; int32_t q_off, c_off, gate_off, up_off;
+    int32_t n_heads, dim, rot_dim, kv_rank, rot_n, n_ff;
+    const float* c_gain; float eps; const float* freq; float rot_mag;
+    void* q_plain; int64_t ld_qp; void* q_lat; int64_t ld_ql; void* hid; int64_t ld_hid; int32_t hid_off;
+    void* cache; const int32_t* block_table; int32_t bt_stride;
+    const int32_t* tok_slot; const int32_t* tok_pos; int32_t T;
+    int32_t act_f32, cache_f32;
+} p3_latent_post_args;
+int p3_latent_post(const p3_latent_post_args* args, cudaStream_t st);
+
+/* out (act) [R, F] = silu(g[r][c]) * u[r][c]; g and u fp32 with the common row pitch ld */
+int p3_glu_silu(const float* g, const float* u, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, cudaStream_t st);
+
+/* router with sigmoid scores: z = Wr x (fp32), s = sigmoid(z), choice = s + correction (correction fp32 [E] or NULL). The E
+ * experts form n_groups equal groups of neighbours (n_groups <= 1: no groups); a group's score is the sum of its two largest
+ * choice scores and only experts of the `keep` best groups can be chosen. ids [T, top] = the `top` largest choice scores among
+ * those (ties: lower index); wts = s[ids] / (sum of them + 1e-20) * scale. */
+int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction, int T, int W, int E,
+                             int top, int n_groups, int keep, float scale, int32_t* ids, float* wts, cudaStream_t st);
+
+/* logits <- cap * tanh(logits * scale / cap) (cap <= 0: logits * scale), n numbers in place */
+int p3_logit_softcap(float* logits, int64_t n, float scale, float cap, cudaStream_t st);
 
 #ifdef __cplusplus
 }

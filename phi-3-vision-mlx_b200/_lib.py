@@ -63,7 +63,7 @@ _SIGS = {
     'p3_rope_table': [_p, _l, _i, _p, _p, _p, _i, _i, _i, _f, _p],
     'p3_embed_gather_xg': [_p, _p, _p, _l, _i, _i, _p, _p, _p, _p],
     # decoders with an fp32 residual stream over a shared page pool (csrc/seq_ops.cu)
-    'p3_embed_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _i, _p],
+    'p3_embed_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _i, _f, _l, _p],
     'p3_postnorm_residual': [_p, _l, _p, _p, _p, _p, _i, _l, _i, _f, _p],
     'p3_rmsnorm_rows_f32': [_p, _p, _p, _p, _i, _l, _i, _f, _p],
     'p3_glu_clamped': [_p, _l, _p, _l, _i, _l, _i, _f, _f, _p, _p],
@@ -72,8 +72,13 @@ _SIGS = {
     'p3_moe_combine': [_p, _l, _p, _p, _i, _p, _l, _i, _p],
     'p3_gather_rows': [_p, _l, _i, _p, _i, _p, _l, _i, _p],
     'p3_distance_penalty_table': [_p, _p, _p, _i, _i, _p],
+    # single-norm parallel layers, latent-vector attention, sigmoid group routing (csrc/seq_ops.cu)
+    'p3_residual_layernorm': [_p, _p, _l, _p, _l, _p, _p, _p, _p, _l, _p, _l, _i, _l, _i, _f, _p],
+    'p3_glu_silu': [_p, _p, _l, _p, _l, _i, _l, _i, _p],
+    'p3_router_sigmoid_groups': [_p, _l, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p],
+    'p3_logit_softcap': [_p, _l, _f, _f, _p],
 }
-_STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode']
+_STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post']
 ATTN_WINDOW_MMA = os.environ.get('P3_ATTN_WINDOW_MMA', '1') != '0'
 
 _lib = None
@@ -191,7 +196,9 @@ class GemmAnyArgs(C.Structure):
                 ('W', _p), ('ldw', _l), ('w_f32', C.c_int32), ('w_group_stride', _l),
                 ('bias', _p), ('bias_group_stride', _l), ('out', _p), ('ldo', _l), ('out_f32', C.c_int32),
                 ('M', _l), ('N', C.c_int32), ('K', C.c_int32), ('seg_offsets', _p), ('n_groups', C.c_int32),
-                ('force_fma', C.c_int32)]
+                ('force_fma', C.c_int32),
+                ('n_batch', C.c_int32), ('x_batch_stride', _l), ('w_batch_stride', _l), ('out_batch_stride', _l),
+                ('gate', _p), ('ld_gate', _l)]
 
 
 class QkvPostArgs(C.Structure):
@@ -211,4 +218,15 @@ class AttnWindowArgs(C.Structure):
                 ('sink', _p), ('penalty', _p), ('n_penalty', C.c_int32), ('gate', _p), ('out', _p), ('ld_out', _l),
                 ('n_heads', C.c_int32), ('n_kv', C.c_int32), ('dim', C.c_int32), ('vdim', C.c_int32), ('scale', C.c_float),
                 ('window', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32), ('tiles', _p), ('n_tiles', C.c_int32),
-                ('n_splits', C.c_int32), ('ws', _p)]
+                ('n_splits', C.c_int32), ('ws', _p), ('v_ld', C.c_int32)]
+
+
+class LatentPostArgs(C.Structure):
+    """p3_latent_post_args (include/phi3_b200.h)"""
+    _fields_ = [('proj', _p), ('ld_proj', _l), ('q_off', C.c_int32), ('c_off', C.c_int32), ('gate_off', C.c_int32), ('up_off', C.c_int32),
+                ('n_heads', C.c_int32), ('dim', C.c_int32), ('rot_dim', C.c_int32), ('kv_rank', C.c_int32), ('rot_n', C.c_int32),
+                ('n_ff', C.c_int32),
+                ('c_gain', _p), ('eps', C.c_float), ('freq', _p), ('rot_mag', C.c_float),
+                ('q_plain', _p), ('ld_qp', _l), ('q_lat', _p), ('ld_ql', _l), ('hid', _p), ('ld_hid', _l), ('hid_off', C.c_int32),
+                ('cache', _p), ('block_table', _p), ('bt_stride', C.c_int32),
+                ('tok_slot', _p), ('tok_pos', _p), ('T', C.c_int32), ('act_f32', C.c_int32), ('cache_f32', C.c_int32)]

@@ -138,3 +138,125 @@ def tiny_tagenex(width=96, vocab=300, layers=None, eps=1e-5):
                   dict(att(6, 3, 24, 24, 33, True), mlp=None),
                   dict(att(3, 3, 32, 24, 100, True), mlp=moe(40, 3, 3))]
     return {'architecture': 'Tagenex', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'layers': layers}
+
+
+# ------------------------------------------------------------------------------------------------ Tapalix
+class TapalixConfig:
+    """config.json of a Tapalix checkpoint: {"architecture": "Tapalix", "vocab", "width", "norm": {"eps"}, "embedding": {"scale"},
+    "layers": [...], "loop": {"start", "stop", "times"} or absent, "logit_scale", "logit_softcap"}.
+    A layer entry has "type" ("latent_attention": per head `dim` plain and `rot_dim` turning query/key numbers with the rotation
+    constants under "rot"; "latent_attention_2": no positions, a sigmoid output gate), "mixer" (heads, dim, vdim, kv_rank, scale,
+    rot_dim, rot: {base, dims, scaling: {factor, original, fast, slow} or absent}) and "mlp": null | {"kind": "moe", expert: {ff},
+    router: {experts, top, scale, groups: {count, keep} or absent}, shared: {ff} or absent}. Nothing is assumed equal between
+    layers. `runs` lists the layer runs in order (a looped layer once per pass): every run has a cache of its own."""
+
+    def __init__(self, d):
+        self.raw = d
+        self.architecture = d.get('architecture', 'Tapalix')
+        self.architectures = [self.architecture]
+        self.vocab_size, self.width = int(d['vocab']), int(d['width'])
+        self.eps = float(d['norm']['eps'])
+        self.embed_scale = float((d.get('embedding') or {}).get('scale', 1.0))
+        self.logit_scale = float(d.get('logit_scale') or 1.0)
+        self.logit_softcap = float(d.get('logit_softcap') or 0.0)
+        self.layers = []
+        for i, lc in enumerate(d['layers']):
+            kind = lc.get('type')
+            if kind not in ('latent_attention', 'latent_attention_2'):
+                raise NotImplementedError(f'layer {i}: mixer type {kind!r} is not part of this design')
+            m = lc['mixer']
+            rotary = kind == 'latent_attention'
+            mixer = SimpleNamespace(kind=kind, rotary=rotary, gated=not rotary, heads=int(m['heads']), dim=int(m['dim']),
+                                    vdim=int(m.get('vdim', m['dim'])), kv_rank=int(m['kv_rank']), scale=float(m['scale']),
+                                    rot_dim=int(m.get('rot_dim', 0)) if rotary else 0, rot=None)
+            if rotary and mixer.rot_dim > 0:
+                r = m['rot']
+                sc = r.get('scaling')
+                mixer.rot = SimpleNamespace(base=float(r['base']), dims=int(r.get('dims', mixer.rot_dim)),
+                                            scaling=None if not sc else SimpleNamespace(
+                                                factor=float(sc['factor']), original=float(sc['original']),
+                                                fast=float(sc['fast']), slow=float(sc['slow'])))
+                if mixer.rot.dims % 2 or not 0 < mixer.rot.dims <= mixer.rot_dim:
+                    raise ValueError(f'layer {i}: rot.dims must be even and at most rot_dim')
+            f = lc.get('mlp')
+            if f is None:
+                ff = None
+            elif f['kind'] == 'moe':
+                r = f['router']
+                g = r.get('groups') or {}
+                sh = f.get('shared') or {}
+                ff = SimpleNamespace(kind='moe', ff=int(f['expert']['ff']), experts=int(r['experts']), top=int(r['top']),
+                                     scale=float(r.get('scale', 1.0)), groups=int(g.get('count', 1)), keep=int(g.get('keep', 1)),
+                                     shared_ff=int(sh.get('ff', 0)))
+                if not 1 <= ff.top <= ff.experts:
+                    raise ValueError(f'layer {i}: top must be in [1, experts]')
+                if ff.groups > 1 and (ff.experts % ff.groups or not 1 <= ff.keep <= ff.groups
+                                      or ff.keep * (ff.experts // ff.groups) < ff.top):
+                    raise ValueError(f'layer {i}: expert groups must divide the experts and the kept ones must hold `top` experts')
+            else:
+                raise NotImplementedError(f"layer {i}: feed-forward kind {f['kind']!r}")
+            self.layers.append(SimpleNamespace(mixer=mixer, ff=ff))
+        self.num_hidden_layers = n = len(self.layers)
+        lp = d.get('loop')
+        if lp:
+            lo, hi, times = int(lp['start']), int(lp['stop']), int(lp['times'])
+            if not (0 <= lo < hi <= n and times >= 1):
+                raise ValueError('loop: need 0 <= start < stop <= layers and times >= 1')
+            self.loop = SimpleNamespace(start=lo, stop=hi, times=times)
+            order = list(range(lo)) + list(range(lo, hi)) * times + list(range(hi, n))
+        else:
+            self.loop, lo, order = None, -1, list(range(n))
+        # (layer index, does a pass of the loop start with this run)
+        self.runs = [(i, i == lo) for i in order]
+
+    def kv_layout(self):
+        """per layer RUN (one shared head, latent + turning key numbers, no separate values): what the page pool allocates"""
+        return [(1, self.layers[i].mixer.kv_rank + self.layers[i].mixer.rot_dim, 0) for i, _ in self.runs]
+
+
+def yarn_frequencies(rot):
+    """angular frequency of every rotated pair and the factor on cos / sin. Pair i turns by base^(-2i/dims) per position. With
+    scaling, pairs that complete fewer than `slow` turns over the `original` context are slowed by `factor`, pairs with more than
+    `fast` turns are left alone, and the pairs between are blended linearly in the pair index; cos and sin grow by
+    0.1 ln(factor) + 1."""
+    import math
+    n = rot.dims // 2
+    f = [rot.base ** (-2.0 * i / rot.dims) for i in range(n)]
+    sc = rot.scaling
+    if sc is None:
+        return f, 1.0
+    index_of = lambda turns: rot.dims * math.log(sc.original / (2 * math.pi * turns)) / (2 * math.log(rot.base))
+    lo = max(math.floor(index_of(sc.fast)), 0)
+    hi = min(math.ceil(index_of(sc.slow)), rot.dims - 1)
+    out = []
+    for i in range(n):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f[i] / sc.factor * ramp + f[i] * (1.0 - ramp))
+    return out, 0.1 * math.log(sc.factor) + 1.0
+
+
+def tiny_tapalix(width=96, vocab=300, layers=None, loop=(1, 3, 2), eps=1e-5):
+    """A small Tapalix config dict for tests: sizes deliberately unequal between layers (dim != vdim != kv_rank, rot.dims below
+    rot_dim is not used by the design but head counts, ranks and group shapes differ), one layer without a feed-forward, one
+    without expert groups, one without a shared expert."""
+    rot = lambda dims, factor=4.0: {'base': 10000.0, 'dims': dims,
+                                    'scaling': {'factor': factor, 'original': 64, 'fast': 16.0, 'slow': 2.0}}
+    la = lambda heads, dim, rd, vdim, rank, scale=None: {
+        'type': 'latent_attention',
+        'mixer': dict(heads=heads, dim=dim, rot_dim=rd, vdim=vdim, kv_rank=rank, scale=scale or (dim + rd) ** -0.5, rot=rot(rd))}
+    la2 = lambda heads, dim, vdim, rank, scale=None: {
+        'type': 'latent_attention_2', 'mixer': dict(heads=heads, dim=dim, vdim=vdim, kv_rank=rank, scale=scale or dim ** -0.5)}
+    moe = lambda ff, e, top, groups=None, shared=None, scale=1.5: {
+        'kind': 'moe', 'expert': {'ff': ff},
+        'router': dict(experts=e, top=top, scale=scale, **({'groups': {'count': groups[0], 'keep': groups[1]}} if groups else {})),
+        **({'shared': {'ff': shared}} if shared else {})}
+    if layers is None:
+        layers = [dict(la2(3, 24, 40, 56), mlp=moe(40, 6, 2, (3, 2), 72)),
+                  dict(la(5, 16, 8, 24, 40), mlp=moe(24, 8, 3, (4, 2), 48)),
+                  dict(la2(2, 48, 16, 72), mlp=None),
+                  dict(la(4, 24, 24, 32, 48), mlp=moe(32, 5, 2, None, None))]
+    d = {'architecture': 'Tapalix', 'vocab': vocab, 'width': width, 'norm': {'eps': eps}, 'embedding': {'scale': width ** 0.5},
+         'layers': layers, 'logit_scale': 1.5, 'logit_softcap': 20.0}
+    if loop:
+        d['loop'] = {'start': loop[0], 'stop': loop[1], 'times': loop[2]}
+    return d

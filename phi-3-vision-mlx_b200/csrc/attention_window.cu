@@ -2,6 +2,9 @@
 // penalty: score(i, j) = scale * q_i . k_j - pen[h][i - j], visible when 0 <= i - j < window (window 0: every earlier key),
 // weights = exp(score) / (exp(sink_h) + sum over visible exp(score)); optional per-(token, head) output gate. Head sizes of
 // keys (dim) and values (vdim) are independent run-time numbers (<= 256), grouped-query heads share K/V (head h reads h / (H/G)).
+// With no window, sink or penalty this is plain causal attention; with v_pool == k_pool and v_ld == dim the value of a token is
+// the leading part of its key row, which is how a latent-vector cache (one shared "head" that every query head reads, the
+// up-projections folded into the queries and applied to the outputs) is served.
 //
 // All keys come from the page pools ([page][kv head][64 tokens][dim | vdim], fp32 or bf16): the caller writes the step's own K/V
 // first. Scores, softmax and the P.V sums are fp32 on the FMA pipes in both storage modes, which is what the all-fp32 serving mode
@@ -32,6 +35,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
     const int d = a.dim, dv = a.vdim, dp = (d + 3) & ~3;       // q rows padded to float4
+    const int vld = a.v_ld > 0 ? a.v_ld : dv;                // pitch of the value rows in a page
     float* Qs = sm;                                          // [BQ][dp]
     float* Ks = Qs + BQ * dp;                                // [64][dp + 1]
     float* Vs = Ks + P3_PAGE * (dp + 1);                     // [64][dv]
@@ -60,10 +64,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     for (int pg = first / P3_PAGE; pg <= last / P3_PAGE; pg++) {
         const int page = bt[pg];
         const CT* kp = (const CT*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
-        const CT* vp = (const CT*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
+        const CT* vp = (const CT*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld;
         __syncthreads();                                     // previous tile fully consumed (and Qs written, first time)
         for (int i = tid; i < P3_PAGE * d; i += blockDim.x) Ks[(i / d) * (dp + 1) + (i % d)] = ldv(kp + i);
-        for (int i = tid; i < P3_PAGE * dv; i += blockDim.x) Vs[i] = ldv(vp + i);
+        for (int i = tid; i < P3_PAGE * dv; i += blockDim.x) Vs[i] = ldv(vp + (size_t)(i / dv) * vld + (i % dv));
         __syncthreads();
         // scores: this warp's RPW rows x keys (lane, lane + 32)
         float s[RPW][2];
@@ -157,13 +161,13 @@ __device__ __forceinline__ float ex2f(float x) {
 }
 
 // 64 rows of a page (row-major, `chunks` 16-byte pieces per row) -> shared memory rows of pitch ld, by 128 threads: LPR lanes per
-// row (chunks <= LPR), no division in the address arithmetic
+// row (chunks <= LPR), no division in the address arithmetic; src_ld = elements between the rows of the source
 template <int LPR>
-__device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, int chunks, int tid) {
+__device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, int chunks, int tid, int src_ld) {
     const int c = tid % LPR, r0 = tid / LPR;
     if (c < chunks) {
 #pragma unroll
-        for (int r = r0; r < P3_PAGE; r += 128 / LPR) cp_async16(smem_u32(dst + r * ld + c * 8), src + (r * chunks + c) * 8);
+        for (int r = r0; r < P3_PAGE; r += 128 / LPR) cp_async16(smem_u32(dst + r * ld + c * 8), src + r * src_ld + c * 8);
     }
 }
 
@@ -182,7 +186,7 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
-    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8;
+    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, vld = a.v_ld > 0 ? a.v_ld : dv;
     const int stage_elems = P3_PAGE * (ldk + ldv);           // bf16 elements of one stage: K [64][ldk] then V [64][ldv]
     bf16* kv_s = reinterpret_cast<bf16*>(smraw);
     float* pen_s = reinterpret_cast<float*>(kv_s + 2 * stage_elems);   // [2][128]
@@ -201,11 +205,11 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
     auto stage_page = [&](int pg, int st) {                  // all threads: issue the copies of page pg into stage st
         const int page = bt[pg];
         const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
-        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * dv;
+        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld;
         bf16* Ks = kv_s + st * stage_elems;
         bf16* Vs = Ks + P3_PAGE * ldk;
-        stage_rows<2 * DK>(Ks, ldk, kp, kc, tid);
-        stage_rows<DN>(Vs, ldv, vp, vc, tid);
+        stage_rows<2 * DK>(Ks, ldk, kp, kc, tid, d);
+        stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
         // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63); plain store, made visible by the barrier
         // that follows the wait for this stage
         const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
-    const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv, G = a.n_kv;
+    const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : dv;
     float* Qs = sm;                                          // [RMAX][d]
     float* Ms = Qs + RMAX * d;                               // [DW][RMAX]
     float* Ls = Ms + DW * RMAX;                              // [DW][RMAX]
@@ -459,7 +463,7 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
 #pragma unroll
                 for (int u = 0; u < VR; u++) {
                     const int kp2 = min(kb + k0 + u, k_hi - 1);
-                    const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * dv;
+                    const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * vld;
 #pragma unroll
                     for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[u][j] = c < dv ? ldv(vp + c) : 0.f; }
                 }
@@ -542,7 +546,7 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
-    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv;
+    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : dv;
     const int pr = min(rep, 16);                             // penalty rows per stage
     const int stage_bytes = P3_PAGE * (ldk + ldv) * 2 + pr * P3_PAGE * 4;   // K [64][ldk], V [64][ldv] (bf16), penalties [pr][64] (fp32)
     float* Ms = reinterpret_cast<float*>(smraw);             // after the stream: [4 warps][16 rows] maxima, sums, [4][16][dv] vectors
@@ -565,11 +569,11 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
         const int nr = min(16, rep - h0), hb = g * rep + h0;
         auto stage_page = [&](int pg, int page, int st) {
             const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * G + g) * P3_PAGE * d;
-            const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * dv;
+            const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * vld;
             bf16* Ks = reinterpret_cast<bf16*>(smraw + (size_t)st * stage_bytes);
             bf16* Vs = Ks + P3_PAGE * ldk;
-            stage_rows<2 * DK>(Ks, ldk, kp, kc, tid);
-            stage_rows<DN>(Vs, ldv, vp, vc, tid);
+            stage_rows<2 * DK>(Ks, ldk, kp, kc, tid, d);
+            stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
             if (a.penalty) {
                 float* Ps = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);
                 for (int i = tid; i < nr * P3_PAGE; i += 128) {
@@ -753,6 +757,7 @@ int check_args(const p3_attn_window_args* a, const char* who) {
     P3_CHECK_ARG(a->dim >= 1 && a->dim <= 256 && a->vdim >= 1 && a->vdim <= 256, "%s: head sizes must be in [1, 256]", who);
     P3_CHECK_ARG(!a->penalty || a->n_penalty >= 1, "%s: empty penalty table", who);
     P3_CHECK_ARG(a->act_f32 == a->cache_f32, "%s: activations and cache must both be fp32 or both bf16", who);
+    P3_CHECK_ARG(a->v_ld == 0 || a->v_ld >= a->vdim, "%s: the value row pitch must hold a value row", who);
     return 0;
 }
 
@@ -800,7 +805,7 @@ static bool prefill_mma_ok(const p3_attn_window_args* a) {
     if (off < 0) { const char* e = getenv("P3_ATTN_WINDOW_MMA"); off = (e && e[0] == '0') ? 1 : 0; }
     return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 128 && a->vdim <= 128 &&
            a->ld_q % 2 == 0 && a->ld_out % 2 == 0 && ((uintptr_t)a->q & 3) == 0 && ((uintptr_t)a->out & 3) == 0 &&
-           ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0;
+           ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0 && a->v_ld % 8 == 0;
 }
 
 static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {

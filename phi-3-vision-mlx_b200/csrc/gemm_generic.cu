@@ -2,7 +2,8 @@
 // accumulation in ascending k (one FMA chain per output element, so a row's result does not depend on which other rows share
 // the launch). Two extras make it the mixture-of-experts workhorse: the rows of X can be gathered through an index list, and
 // the rows can be cut into segments that each multiply with their own weight matrix (device-side segment offsets, so the host
-// never learns how many tokens an expert received).
+// never learns how many tokens an expert received). A launch can also hold a batch of independent products over column blocks of
+// X and out (one per attention head), with an optional sigmoid gate on the result.
 //
 // fp32 operands run on the FMA pipes (this is the "true 32-bit" path: no TF32). bf16 operands of aligned shapes run on the
 // tensor cores through mma.sync m16n8k16 (fp32 accumulators); the dense bf16 projections with K % 8 == 0 go to the tcgen05
@@ -20,6 +21,7 @@ struct AnyP {
     void* out; int64_t ldo;
     int64_t M; int N, K;
     const int32_t* seg; int n_groups;
+    int64_t x_bs, w_bs, o_bs; const float* gate; int64_t ld_gate;     // blockIdx.z = product of a batch (column blocks of X and out)
 };
 
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
@@ -51,8 +53,8 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
     int g; int64_t m0, m1;
     if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
     const int n0 = blockIdx.y * BN, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const XT* X = (const XT*)p.X;
-    const WT* W = (const WT*)p.W + (size_t)g * p.w_gstride;
+    const XT* X = (const XT*)p.X + (size_t)blockIdx.z * p.x_bs;
+    const WT* W = (const WT*)p.W + (size_t)g * p.w_gstride + (size_t)blockIdx.z * p.w_bs;
     // this thread stages row (tid / 4) of each tile, k = (tid % 4) * 4 .. + 3
     const int lr = tid >> 2, lk = (tid & 3) * 4;
     const int64_t am = m0 + lr;
@@ -81,7 +83,8 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
         __syncthreads();
     }
     const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
-    OT* out = (OT*)p.out;
+    OT* out = (OT*)p.out + (size_t)blockIdx.z * p.o_bs;
+    const float* gate = p.gate ? p.gate + (size_t)blockIdx.z * p.o_bs : nullptr;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int64_t m = m0 + ty * 4 + i;
@@ -89,7 +92,10 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n < p.N) stf(out + (size_t)m * p.ldo + n, acc[i][j] + (bias ? bias[n] : 0.f));
+            if (n >= p.N) continue;
+            float v = acc[i][j] + (bias ? bias[n] : 0.f);
+            if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)m * p.ld_gate + n]));
+            stf(out + (size_t)m * p.ldo + n, v);
         }
     }
 }
@@ -110,8 +116,8 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
     const int n0 = blockIdx.y * BN, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
-    const bf16* X = (const bf16*)p.X;
-    const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride;
+    const bf16* X = (const bf16*)p.X + (size_t)blockIdx.z * p.x_bs;
+    const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride + (size_t)blockIdx.z * p.w_bs;
     // staging: 64 rows x 16 chunks of 8 elements per operand; round j: row 8 j + 2 warp + lane / 16, chunk lane % 16
     const int srow0 = 2 * warp + (lane >> 4), schunk = (lane & 15) * 8;
     int64_t aoff[8];                                        // element offset of this thread's A row in round j, -1: no such row
@@ -167,7 +173,8 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
         __syncthreads();
     }
     const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
-    OT* out = (OT*)p.out;
+    OT* out = (OT*)p.out + (size_t)blockIdx.z * p.o_bs;
+    const float* gate = p.gate ? p.gate + (size_t)blockIdx.z * p.o_bs : nullptr;
 #pragma unroll
     for (int i = 0; i < 2; i++)
 #pragma unroll
@@ -176,7 +183,11 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
             for (int e = 0; e < 4; e++) {
                 const int64_t m = m0 + wm + i * 16 + (lane >> 2) + (e >> 1) * 8;
                 const int n = n0 + wn + j * 8 + (lane & 3) * 2 + (e & 1);
-                if (m < m1 && n < p.N) stf(out + (size_t)m * p.ldo + n, acc[i][j][e] + (bias ? bias[n] : 0.f));
+                if (m < m1 && n < p.N) {
+                    float v = acc[i][j][e] + (bias ? bias[n] : 0.f);
+                    if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)m * p.ld_gate + n]));
+                    stf(out + (size_t)m * p.ldo + n, v);
+                }
             }
 }
 }  // namespace
@@ -189,14 +200,19 @@ extern "C" int p3_gemm_any(const p3_gemm_any_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a->x_f32 == a->w_f32, "gemm_any: X and W must have the same element type");
     if (a->M == 0) return 0;
     AnyP p{a->X, a->ldx, a->x_rows, a->x_row_div, a->W, a->ldw, a->w_group_stride, a->bias, a->bias_group_stride,
-           a->out, a->ldo, a->M, a->N, a->K, a->seg_offsets, a->seg_offsets ? a->n_groups : 1};
+           a->out, a->ldo, a->M, a->N, a->K, a->seg_offsets, a->seg_offsets ? a->n_groups : 1,
+           a->x_batch_stride, a->w_batch_stride, a->out_batch_stride, a->gate, a->ld_gate};
+    const int nb = a->n_batch > 1 ? a->n_batch : 1;
+    P3_CHECK_ARG(nb <= 65535, "gemm_any: too many products in a batch");
+    if (nb == 1) p.x_bs = p.w_bs = p.o_bs = 0;
     const unsigned mt = (unsigned)((a->M + BM - 1) / BM) + (a->seg_offsets ? (unsigned)a->n_groups : 0u);
-    const dim3 grid(mt, (unsigned)((a->N + BN - 1) / BN));
+    const dim3 grid(mt, (unsigned)((a->N + BN - 1) / BN), (unsigned)nb);
     if (a->x_f32) {
         if (a->out_f32) p3_launch_pdl(gemm_any_fma_kernel<float, float, float>, dim3(grid), dim3(256), (size_t)(0), st, p);
         else p3_launch_pdl(gemm_any_fma_kernel<float, float, bf16>, dim3(grid), dim3(256), (size_t)(0), st, p);
     } else {
         const bool tc = a->K % 8 == 0 && a->ldx % 8 == 0 && a->ldw % 8 == 0 && a->w_group_stride % 8 == 0 &&
+                        (nb == 1 || (a->x_batch_stride % 8 == 0 && a->w_batch_stride % 8 == 0)) &&
                         ((uintptr_t)a->X & 15) == 0 && ((uintptr_t)a->W & 15) == 0 && !a->force_fma;
         if (tc) {
             if (a->out_f32) p3_launch_pdl(gemm_any_mma_kernel<float>, dim3(grid), dim3(128), (size_t)(0), st, p);

@@ -35,7 +35,7 @@ constexpr int RPT = 8;
 
 template <typename AT>
 __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ x,
-                                  AT* __restrict__ xa, int W, int vocab) {
+                                  AT* __restrict__ xa, int W, int vocab, float scale, int64_t ldxa) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     const int64_t t = blockIdx.x;
@@ -45,11 +45,11 @@ __global__ void embed_rows_kernel(const bf16* __restrict__ table, const int32_t*
     for (int i0 = threadIdx.x; i0 < W; i0 += RPT * blockDim.x) {
         float v[RPT];
 #pragma unroll
-        for (int k = 0; k < RPT; k++) { const int i = i0 + k * blockDim.x; v[k] = i < W ? __bfloat162float(src[i]) : 0.f; }
+        for (int k = 0; k < RPT; k++) { const int i = i0 + k * blockDim.x; v[k] = i < W ? __bfloat162float(src[i]) * scale : 0.f; }
 #pragma unroll
         for (int k = 0; k < RPT; k++) {
             const int i = i0 + k * blockDim.x;
-            if (i < W) { x[(size_t)t * W + i] = v[k]; if (xa) stv(xa + (size_t)t * W + i, v[k]); }
+            if (i < W) { x[(size_t)t * W + i] = v[k]; if (xa) stv(xa + (size_t)t * ldxa + i, v[k]); }
         }
     }
 }
@@ -349,13 +349,236 @@ __global__ void distance_penalty_kernel(const float* __restrict__ r1, const floa
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         pen[(size_t)h * n + i] = r1[h] * log1pf(r2[h] * (float)i);
 }
+
+// ---------------------------------------------------------------- v = x + add1 + add2 ; x <- v ; activation copy ; layer norm of v
+// One CTA per row. Mean and variance are two passes over the row's fp32 sums (the variance is the mean squared deviation, not
+// E[v^2] - mean^2). The first RPT * blockDim elements stay in registers; longer rows are formed again from memory in each pass
+// (x is written only in the last one).
+template <typename AT>
+__global__ void residual_layernorm_kernel(float* x, const float* __restrict__ a1, int64_t ld1, const float* __restrict__ a2, int64_t ld2,
+                                          const int32_t* __restrict__ rows, const float* __restrict__ gain, const float* __restrict__ bias,
+                                          AT* __restrict__ xa, int64_t ldxa, AT* __restrict__ ho, int64_t ldh, int W, float eps) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    __shared__ float sh[32];
+    const int64_t r = blockIdx.x, t = rows ? rows[r] : r;
+    float* xr = x + (size_t)t * W;
+    const float* p1 = a1 ? a1 + (size_t)t * ld1 : nullptr;
+    const float* p2 = a2 ? a2 + (size_t)t * ld2 : nullptr;
+    const int nt = blockDim.x;
+    auto val = [&](int i) { float u = xr[i]; if (p1) u += p1[i]; if (p2) u += p2[i]; return u; };
+    float v[RPT];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; v[k] = i < W ? val(i) : 0.f; s += v[k]; }
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) s += val(i);
+    const bool store_x = !rows && (p1 || p2);
+    float mean = 0.f, rstd = 0.f;
+    if (ho) {
+        mean = block_sum(s, sh) / (float)W;
+        float q = 0.f;
+#pragma unroll
+        for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; const float dlt = v[k] - mean; if (i < W) q = fmaf(dlt, dlt, q); }
+        for (int i = threadIdx.x + RPT * nt; i < W; i += nt) { const float dlt = val(i) - mean; q = fmaf(dlt, dlt, q); }
+        rstd = 1.0f / sqrtf(block_sum(q, sh) / (float)W + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) {
+        const int i = threadIdx.x + k * nt;
+        if (i >= W) continue;
+        if (store_x) xr[i] = v[k];
+        if (xa) stv(xa + (size_t)r * ldxa + i, v[k]);
+        if (ho) stv(ho + (size_t)r * ldh + i, (v[k] - mean) * rstd * gain[i] + bias[i]);
+    }
+    for (int i = threadIdx.x + RPT * nt; i < W; i += nt) {
+        const float u = val(i);
+        if (store_x) xr[i] = u;
+        if (xa) stv(xa + (size_t)r * ldxa + i, u);
+        if (ho) stv(ho + (size_t)r * ldh + i, (u - mean) * rstd * gain[i] + bias[i]);
+    }
+}
+
+// ---------------------------------------------------------------- latent attention: what follows the fused input projection
+// Grid (token, job group). Jobs of a token: 0 = the latent vector (RMS norm -> cache) with the shared turning key part
+// (rotation -> cache), 1 .. H = the query heads (plain part -> q_plain, turning part rotated -> q_lat), H + 1 .. = slabs of 1024
+// columns of the gated unit. One warp per job.
+__device__ __forceinline__ void turn_pair(float u, float v, float ang, float mag, float& ou, float& ov) {
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    sn *= mag; cs *= mag;
+    ou = u * cs - v * sn;
+    ov = v * cs + u * sn;
+}
+
+template <typename AT, typename CT>
+__global__ void latent_post_kernel(p3_latent_post_args a) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* pr = a.proj + (size_t)t * a.ld_proj;
+    const int slot = a.tok_slot[t], pos = a.tok_pos[t];
+    const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
+    const int H = a.n_heads, d = a.dim, dr = a.rot_dim, R = a.kv_rank, half = a.rot_n / 2;
+    const int ff_jobs = (a.n_ff + 1023) / 1024;
+    const float fpos = (float)pos;
+    for (int job = blockIdx.y * nw + warp; job < 1 + H + ff_jobs; job += gridDim.y * nw) {
+        if (job == 0) {
+            const float* c = pr + a.c_off;
+            CT* dst = (CT*)a.cache + ((size_t)page * P3_PAGE + off) * (R + dr);
+            float ss = 0.f;
+            for (int i = lane; i < R; i += 32) ss = fmaf(c[i], c[i], ss);
+            ss = warp_sum(ss);
+            const float rs = 1.0f / sqrtf(ss / (float)R + a.eps);
+            for (int i = lane; i < R; i += 32) stv(dst + i, c[i] * rs * a.c_gain[i]);
+            const float* kr = c + R;
+            for (int i = lane; i < half; i += 32) {
+                float ou, ov;
+                turn_pair(kr[i], kr[i + half], fpos * a.freq[i], a.rot_mag, ou, ov);
+                stv(dst + R + i, ou); stv(dst + R + half + i, ov);
+            }
+            for (int i = a.rot_n + lane; i < dr; i += 32) stv(dst + R + i, kr[i]);
+        } else if (job <= H) {
+            const int h = job - 1;
+            const float* q = pr + a.q_off + (size_t)h * (d + dr);
+            AT* qp = (AT*)a.q_plain + (size_t)t * a.ld_qp + (size_t)h * d;
+            for (int i = lane; i < d; i += 32) stv(qp + i, q[i]);
+            if (dr > 0) {
+                const float* qr = q + d;
+                AT* ql = (AT*)a.q_lat + (size_t)t * a.ld_ql + (size_t)h * (R + dr) + R;
+                for (int i = lane; i < half; i += 32) {
+                    float ou, ov;
+                    turn_pair(qr[i], qr[i + half], fpos * a.freq[i], a.rot_mag, ou, ov);
+                    stv(ql + i, ou); stv(ql + half + i, ov);
+                }
+                for (int i = a.rot_n + lane; i < dr; i += 32) stv(ql + i, qr[i]);
+            }
+        } else {
+            const int c0 = (job - 1 - H) * 1024, c1 = min(a.n_ff, c0 + 1024);
+            AT* hd = (AT*)a.hid + (size_t)t * a.ld_hid + a.hid_off;
+            for (int i = c0 + lane; i < c1; i += 32) {
+                const float g = pr[a.gate_off + i], u = pr[a.up_off + i];
+                stv(hd + i, g / (1.0f + expf(-g)) * u);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- y = silu(g) * u
+template <typename AT>
+__global__ void glu_silu_kernel(const float* __restrict__ g, const float* __restrict__ u, int64_t ld, AT* __restrict__ out, int64_t ldo,
+                                int64_t R, int F) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int64_t n = R * F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F; const int c = (int)(i % F);
+        const float gv = g[(size_t)r * ld + c], uv = u[(size_t)r * ld + c];
+        stv(out + (size_t)r * ldo + c, gv / (1.0f + expf(-gv)) * uv);
+    }
+}
+
+// ---------------------------------------------------------------- router with sigmoid scores, a choice correction and expert groups
+// One CTA per token; the logits are formed as in router_topk_kernel (eight experts per pass, fixed summation order). Warp 0 then
+// selects: group scores (sum of the two largest choice scores of a group), the `keep` best groups, the `top` best experts of
+// those; every maximum is an arg-max over the warp with ties going to the lower index.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+template <typename AT>
+__global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr,
+                                             const float* __restrict__ corr, int W, int E, int top, int n_groups, int keep,
+                                             float scale, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    extern __shared__ float z[];                             // [E] scores s, [E] choice scores, [groups] group scores, [warps][8] partial sums
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = blockIdx.x, NG = n_groups > 1 ? n_groups : 1, gs = E / NG;
+    float* ch = z + E;
+    float* gsc = ch + E;
+    float* part = gsc + NG;
+    const AT* xr = x + (size_t)t * ldx;
+    for (int e0 = 0; e0 < E; e0 += 8) {
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const int ne = min(8, E - e0);
+#pragma unroll 2
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const float xv = ldv(xr + i);
+            float wv[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) wv[j] = j < ne ? Wr[(size_t)(e0 + j) * W + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[j] = fmaf(xv, wv[j], s[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float v = warp_sum(s[j]);
+            if (lane == 0) part[warp * 8 + j] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < ne) {
+            float v = 0.f;
+            for (int w = 0; w < nw; w++) v += part[w * 8 + threadIdx.x];
+            const float sg = 1.0f / (1.0f + expf(-v));
+            z[e0 + threadIdx.x] = sg;
+            ch[e0 + threadIdx.x] = sg + (corr ? corr[e0 + threadIdx.x] : 0.f);
+        }
+        __syncthreads();
+    }
+    if (warp != 0) return;
+    if (NG > 1) {
+        for (int g = lane; g < NG; g += 32) {                // a group's score: its two largest choice scores
+            float b1 = -INFINITY, b2 = -INFINITY;
+            for (int e = g * gs; e < (g + 1) * gs; e++) { const float c = ch[e]; if (c > b1) { b2 = b1; b1 = c; } else if (c > b2) b2 = c; }
+            gsc[g] = gs > 1 ? b1 + b2 : b1;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep; k++) {                     // mark the kept groups by +inf, one arg-max per kept group
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < NG; g += 32) { const float c = gsc[g]; if (c != INFINITY && (c > bv || (c == bv && g < bi))) { bv = c; bi = g; } }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi < NG) gsc[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32) if (gsc[e / gs] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    float den = 0.f;
+    for (int j = 0; j < top; j++) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { const float c = ch[e]; if (!isnan(c) && (c > bv || (c == bv && e < bi))) { bv = c; bi = e; } }
+        warp_argmax(bv, bi);
+        if (bi >= E) bi = 0;                                  // fewer selectable experts than `top`: cannot happen with valid configs
+        if (lane == 0) { ids[(size_t)t * top + j] = bi; wts[(size_t)t * top + j] = z[bi]; ch[bi] = NAN; }
+        den += z[bi];
+        __syncwarp();
+    }
+    const float f = scale / (den + 1e-20f);
+    for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= f;
+}
+
+// ---------------------------------------------------------------- logits <- cap * tanh(logits * scale / cap)
+__global__ void logit_softcap_kernel(float* __restrict__ lg, int64_t n, float scale, float cap) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = lg[i] * scale;
+        lg[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+    }
+}
 }  // namespace
 
 extern "C" int p3_embed_rows_f32(const void* table, const int32_t* ids, float* x, void* x_act, int act_f32, int64_t T, int W, int vocab,
-                                 cudaStream_t st) {
+                                 float scale, int64_t ld_act, cudaStream_t st) {
     if (T == 0) return 0;
-    if (act_f32) p3_launch_pdl(embed_rows_kernel<float>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (float*)x_act, W, vocab);
-    else p3_launch_pdl(embed_rows_kernel<bf16>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (bf16*)x_act, W, vocab);
+    if (ld_act <= 0) ld_act = W;
+    if (act_f32) p3_launch_pdl(embed_rows_kernel<float>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (float*)x_act, W, vocab, scale, ld_act);
+    else p3_launch_pdl(embed_rows_kernel<bf16>, dim3((unsigned)T), dim3(128), (size_t)(0), st, (const bf16*)table, ids, x, (bf16*)x_act, W, vocab, scale, ld_act);
     P3_CHECK_LAUNCH("embed_rows_f32");
     return 0;
 }
@@ -454,5 +677,70 @@ extern "C" int p3_distance_penalty_table(const float* r1, const float* r2, float
     P3_CHECK_ARG(H >= 1 && n >= 1, "distance_penalty_table: empty");
     p3_launch_pdl(distance_penalty_kernel, dim3(dim3((unsigned)((n + 255) / 256), (unsigned)H)), dim3(256), (size_t)(0), st, r1, r2, pen, H, n);
     P3_CHECK_LAUNCH("distance_penalty_table");
+    return 0;
+}
+
+extern "C" int p3_residual_layernorm(float* x, const float* add1, int64_t ld1, const float* add2, int64_t ld2, const int32_t* rows,
+                                     const float* gain, const float* bias, void* x_act, int64_t ld_xact, void* h_out, int64_t ld_h,
+                                     int act_f32, int64_t R, int W, float eps, cudaStream_t st) {
+    P3_CHECK_ARG(x && W >= 1, "residual_layernorm: null argument");
+    P3_CHECK_ARG(!h_out || (gain && bias), "residual_layernorm: the norm needs weight and bias");
+    if (R == 0) return 0;
+    const int th = W > 4096 ? 1024 : W > 2048 ? 512 : W >= 1024 ? 256 : 128;
+    if (act_f32) p3_launch_pdl(residual_layernorm_kernel<float>, dim3((unsigned)R), dim3(th), (size_t)(0), st, x, add1, ld1, add2, ld2, rows, gain, bias,
+                               (float*)x_act, ld_xact, (float*)h_out, ld_h, W, eps);
+    else p3_launch_pdl(residual_layernorm_kernel<bf16>, dim3((unsigned)R), dim3(th), (size_t)(0), st, x, add1, ld1, add2, ld2, rows, gain, bias,
+                       (bf16*)x_act, ld_xact, (bf16*)h_out, ld_h, W, eps);
+    P3_CHECK_LAUNCH("residual_layernorm");
+    return 0;
+}
+
+extern "C" int p3_latent_post(const p3_latent_post_args* a, cudaStream_t st) {
+    P3_CHECK_ARG(a && a->proj && a->q_plain && a->cache && a->c_gain && a->block_table && a->tok_slot && a->tok_pos, "latent_post: null argument");
+    P3_CHECK_ARG(a->rot_dim == 0 || (a->q_lat && a->freq), "latent_post: a turning part needs q_lat and the frequencies");
+    P3_CHECK_ARG(a->rot_n >= 0 && a->rot_n <= a->rot_dim && a->rot_n % 2 == 0, "latent_post: rot_n must be even and <= rot_dim");
+    P3_CHECK_ARG(a->n_ff == 0 || a->hid, "latent_post: the gated unit needs its output");
+    if (a->T == 0) return 0;
+    const int jobs = 1 + a->n_heads + (a->n_ff + 1023) / 1024, th = 128;
+    const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
+    const dim3 grid((unsigned)a->T, (unsigned)groups);
+    if (a->act_f32 && a->cache_f32) p3_launch_pdl(latent_post_kernel<float, float>, dim3(grid), dim3(th), (size_t)(0), st, *a);
+    else if (!a->act_f32 && !a->cache_f32) p3_launch_pdl(latent_post_kernel<bf16, bf16>, dim3(grid), dim3(th), (size_t)(0), st, *a);
+    else P3_CHECK_ARG(false, "latent_post: activations and cache must both be fp32 or both bf16");
+    P3_CHECK_LAUNCH("latent_post");
+    return 0;
+}
+
+extern "C" int p3_glu_silu(const float* g, const float* u, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F,
+                           cudaStream_t st) {
+    if (R == 0 || F == 0) return 0;
+    const int64_t n = R * F;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (out_f32) p3_launch_pdl(glu_silu_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (float*)out, ldo, R, F);
+    else p3_launch_pdl(glu_silu_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (bf16*)out, ldo, R, F);
+    P3_CHECK_LAUNCH("glu_silu");
+    return 0;
+}
+
+extern "C" int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction, int T, int W,
+                                        int E, int top, int n_groups, int keep, float scale, int32_t* ids, float* wts, cudaStream_t st) {
+    P3_CHECK_ARG(top >= 1 && top <= E && E <= 1024, "router_sigmoid_groups: need 1 <= top <= experts <= 1024");
+    const int NG = n_groups > 1 ? n_groups : 1;
+    P3_CHECK_ARG(E % NG == 0 && (NG == 1 || (keep >= 1 && keep <= NG && keep * (E / NG) >= top)),
+                 "router_sigmoid_groups: groups must divide the experts and the kept groups must hold `top` experts");
+    if (T == 0) return 0;
+    const int nw = W >= 1024 ? 8 : 4;
+    const size_t sm = ((size_t)2 * E + NG + nw * 8) * sizeof(float);
+    if (x_f32) p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, correction, W, E, top, NG, keep, scale, ids, wts);
+    else p3_launch_pdl(router_sigmoid_groups_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, correction, W, E, top, NG, keep, scale, ids, wts);
+    P3_CHECK_LAUNCH("router_sigmoid_groups");
+    return 0;
+}
+
+extern "C" int p3_logit_softcap(float* logits, int64_t n, float scale, float cap, cudaStream_t st) {
+    if (n == 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    p3_launch_pdl(logit_softcap_kernel, dim3(grid), dim3(256), (size_t)(0), st, logits, n, scale, cap);
+    P3_CHECK_LAUNCH("logit_softcap");
     return 0;
 }

@@ -22,7 +22,7 @@ import torch
 from . import _lib
 from ._lib import call, ptr
 from .paged import PagePool, PoolExhausted, PAGE
-from .tagenex import StepBatch
+from .lm_base import StepBatch
 
 
 

@@ -85,6 +85,18 @@ def _tagenex_build(cfg, weights, device='cuda', dtype=None, **kw):
     return TagenexB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
 
 
+def _tapalix_config(d):
+    from .configs import TapalixConfig
+    return TapalixConfig(d)
+
+
+def _tapalix_build(cfg, weights, device='cuda', dtype=None, **kw):
+    import torch
+    from .tapalix import TapalixB200
+    return TapalixB200(cfg, weights, device=device, dtype=dtype or torch.bfloat16)
+
+
 register('Phi3ForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Phi3VForCausalLM', _phi3_config, _phi3_build, 'batch')
 register('Tagenex', _tagenex_config, _tagenex_build, 'paged')
+register('Tapalix', _tapalix_config, _tapalix_build, 'paged')

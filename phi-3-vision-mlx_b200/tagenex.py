@@ -20,37 +20,15 @@ fp32; positions, penalties, scores, softmax, norms, router, gates, value mixing 
 everything is fp32 on the FMA pipes (no TF32). Dense bf16 products with K % 8 == 0 run on the tcgen05 GEMM (p3_gemm), everything
 else on p3_gemm_any.
 """
-import os
 import torch
 from . import _lib
 from ._lib import call, call_struct, ptr
+from .lm_base import PagedLM, StepBatch, _page_slices, _stream  # noqa: F401  (StepBatch is re-exported for engine.py)
 from .configs import TagenexConfig
 from .paged import PAGE
 
 
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
-
-
-def _page_slices(pairs, pages, slots=2 * 148):
-    """slices of the visible pages per (request, K/V head) for the tensor-core decode attention (two CTAs per SM). Cost model in
-    units of the memory latency: a CTA pays one latency to fill its copy ring and half of one per page after that (two pages in
-    flight); equal CTAs run in whole rounds of the resident ones."""
-    best, best_cost = 1, float('inf')
-    for ns in range(1, max(1, min(pages, 32)) + 1):
-        per = -(-pages // ns)
-        cost = -(-pairs * ns // slots) * (1.0 + per / 2.0)
-        if cost < best_cost - 1e-9:
-            best, best_cost = ns, cost
-    return best
-
-
-class StepBatch:
-    """Device-side description of one engine step (built by engine.Engine.step)."""
-    __slots__ = ('T', 'ids', 'tok_slot', 'tok_pos', 'pf_tiles', 'n_pf', 'dec_tiles', 'n_dec', 'want_rows', 'R', 'max_pos', 'flat')
-
-
-class TagenexB200:
+class TagenexB200(PagedLM):
     arch = 'Tagenex'
 
     def __init__(self, cfg, weights, device='cuda', dtype=torch.bfloat16):
@@ -62,11 +40,8 @@ class TagenexB200:
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError('dtype must be torch.bfloat16 or torch.float32')
         self.cfg, self.dev, self.dtype = cfg, torch.device(device), dtype
-        self.f32 = int(dtype == torch.float32)
         self.W, self.V, self.eps = cfg.width, cfg.vocab_size, cfg.eps
-        self.use_tc = os.environ.get('P3_LM_TC', '1') != '0'
-        self.moe_dense_rows = int(os.environ.get('P3_LM_MOE_DENSE_ROWS', '1024'))   # (token, choice) pairs from which experts run as dense GEMMs
-        self.use_skinny = os.environ.get('P3_LM_SKINNY', '1') != '0' and hasattr(_lib.lib(), 'p3_gemm_skinny')
+        self._init_products()
         w = weights
         mat = lambda t: t.to(self.dev, dtype).contiguous()                     # matrices: the compute type
         f32 = lambda t: t.to(self.dev, torch.float32).contiguous()            # everything that enters fp32 arithmetic
@@ -103,23 +78,10 @@ class TagenexB200:
         # query rows per attention tile the engine cuts prompt portions into: 64 when every layer takes the tensor-core prefill
         # kernel (bf16, key size % 16 == 0, value size % 8 == 0, both <= 128; csrc/attention_window.cu), else 32
         self.q_tile = 64 if all(L['mma'] for L in self.layers) else 32
-        self.profile = None      # bench.py: list of (kind, ev0, ev1, flops, bytes) when instrumenting
-
-    def _ev(self, start=None, kind=None, flops=0, nbytes=0):
-        if self.profile is None:
-            return None
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        if start is not None:
-            self.profile.append((kind, start, e, flops, nbytes))
-        return e
 
     # ------------------------------------------------------------------ what the engine asks of a model
     def kv_layout(self):
         return self.cfg.kv_layout()
-
-    def cache_dtype(self):
-        return self.dtype
 
     def prepare(self, max_context):
         """distance-penalty tables r1_h ln(1 + r2_h d) for every distance a query can see: d < window, or < the longest
@@ -137,56 +99,7 @@ class TagenexB200:
 
     def graph_safe(self, b):
         """may this step be captured as a CUDA graph? Not when a mixture layer would read its segment offsets back."""
-        return all(l.ff is None or l.ff.kind != 'moe' or b.T * l.ff.top < self.moe_dense_rows or self.f32 or not self.use_tc
-                   for l in self.cfg.layers)
-
-    # ------------------------------------------------------------------ matrix products
-    def linear(self, x, w, out, bias32=None, bias16=None, nxt=None):
-        """out[M,N] (fp32 or act type, by out.dtype) = x[M,K] w[N,K]^T (+ bias). Returns the bias (fp32) that is STILL TO ADD: None
-        when the product added it, bias32 when the kernel has no bias input (the weight-streaming kernel of small batches); the
-        consumer kernel (activation / output norm) then adds it. `nxt`: the matrix of the next product; the weight-streaming
-        kernel pulls its first megabytes into L2 so that they arrive while the small kernels in between run."""
-        M, K = x.shape
-        N = w.shape[0]
-        ev = self._ev()
-        try:
-            return self._linear(x, w, out, bias32, bias16, nxt)
-        finally:
-            self._ev(ev, 'gemm', 2 * M * N * K, w.numel() * w.element_size() + x.numel() * x.element_size() + out.numel() * out.element_size())
-
-    L2_PREFETCH_CAP = int(os.environ.get('P3_LM_PF_CAP_MB', '16')) << 20
-
-    def _linear(self, x, w, out, bias32=None, bias16=None, nxt=None):
-        M, K = x.shape
-        N = w.shape[0]
-        aligned = (not self.f32 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-        if (self.use_skinny and aligned and M <= 16 and K % 64 == 0 and N % 16 == 0 and out.dtype == torch.float32
-                and w.is_contiguous()):
-            # <= 16 tokens: the product is a stream of the weights; the Phi-3 decode kernel does that at HBM speed
-            pf = 0 if nxt is None else min(nxt.numel() * nxt.element_size(), self.L2_PREFETCH_CAP)
-            call('p3_gemm_skinny', ptr(x), x.stride(0), None, self.eps, ptr(w), ptr(out), out.stride(0), None, M, N, K,
-                 _lib.EPI_F32, None, 0, None, ptr(nxt) if pf else None, pf, _stream())
-            return bias32
-        if self.use_tc and aligned and (bias32 is None or bias16 is not None):
-            epi = _lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_NONE
-            call('p3_gemm', ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias16), ptr(out), out.stride(0), None, None,
-                 M, N, K, epi, 0, _stream())
-            return None
-        self.gemm_any(x, w, out, bias32)
-        return None
-
-    def gemm_any(self, x, w, out, bias=None, rows=None, row_div=1, seg=None, n_groups=0, M=None):
-        a = _lib.GemmAnyArgs()
-        a.X, a.ldx, a.x_f32 = ptr(x), x.stride(0), self.f32
-        a.x_rows, a.x_row_div = ptr(rows), row_div
-        a.W, a.ldw, a.w_f32 = ptr(w), w.stride(-2), self.f32
-        a.w_group_stride = w.stride(0) if w.dim() == 3 else 0
-        a.bias, a.bias_group_stride = ptr(bias), (bias.stride(0) if bias is not None and bias.dim() == 2 else 0)
-        a.out, a.ldo, a.out_f32 = ptr(out), out.stride(0), int(out.dtype == torch.float32)
-        a.M, a.N, a.K = (x.shape[0] if M is None else M), w.shape[-2], w.shape[-1]
-        a.seg_offsets, a.n_groups = ptr(seg), n_groups
-        call_struct('p3_gemm_any', a, _stream())
-        return out
+        return not any(l.ff is not None and l.ff.kind == 'moe' and self.experts_dense(l.ff, b.T) for l in self.cfg.layers)
 
     # ------------------------------------------------------------------ one engine step
     def forward(self, b, pool, trace=None):
@@ -196,7 +109,7 @@ class TagenexB200:
         act = self.dtype
         e = lambda *s, dt=torch.float32: torch.empty(s, dtype=dt, device=dev)
         x, xa = e(T, W), e(T, W, dt=act)
-        call('p3_embed_rows_f32', ptr(self.embed), ptr(b.ids), ptr(x), ptr(xa), self.f32, T, W, self.V, st)
+        call('p3_embed_rows_f32', ptr(self.embed), ptr(b.ids), ptr(x), ptr(xa), self.f32, T, W, self.V, 1.0, W, st)
         v_first = None
         y = e(T, W)
         for li, L in enumerate(self.layers):
@@ -275,46 +188,12 @@ class TagenexB200:
         return logits
 
     def _moe(self, L, f, xa, y, T):
-        """top-k mixture: route, sort the (token, choice) pairs by expert, two grouped products over the sorted rows, combine"""
-        st, dev, n = _stream(), self.dev, T * f.top
-        ids = torch.empty((T, f.top), dtype=torch.int32, device=dev)
-        wts = torch.empty((T, f.top), dtype=torch.float32, device=dev)
+        """top-k mixture: route (softmax over the chosen logits), then the grouped expert products of the base class"""
+        st = _stream()
+        ids = torch.empty((T, f.top), dtype=torch.int32, device=self.dev)
+        wts = torch.empty((T, f.top), dtype=torch.float32, device=self.dev)
         call('p3_router_topk', ptr(xa), xa.stride(0), self.f32, ptr(L['router']), ptr(L['router_b']), T, self.W, f.experts, f.top,
              ptr(ids), ptr(wts), st)
-        seg = torch.empty(f.experts + 1, dtype=torch.int32, device=dev)
-        order = torch.empty(n, dtype=torch.int32, device=dev)
-        where = torch.empty(n, dtype=torch.int32, device=dev)
-        call('p3_moe_sort', ptr(ids), n, f.experts, ptr(seg), ptr(order), ptr(where), st)
-        gu = torch.empty((n, 2 * f.ff), dtype=torch.float32, device=dev)
-        hid = torch.empty((n, f.ff), dtype=self.dtype, device=dev)
-        dn = torch.empty((n, self.W), dtype=torch.float32, device=dev)
-        # Large batches (prompt portions): the segment offsets are read back (one small D2H per mixture layer) and every expert's
-        # rows go through the tcgen05 GEMM as a dense product over the gathered, expert-ordered activations. Small batches stay
-        # on the device-side grouped kernel, which needs no host knowledge of the counts.
-        dense = (self.use_tc and not self.f32 and n >= self.moe_dense_rows and self.W % 8 == 0 and f.ff % 8 == 0)
-        ev = self._ev()
-        if dense:
-            xs = torch.empty((n, self.W), dtype=self.dtype, device=dev)
-            call('p3_gather_rows', ptr(xa), xa.stride(0), self.f32, ptr(order), f.top, ptr(xs), n, self.W, st)
-            cut = seg.tolist()
-            for ex in range(f.experts):
-                a0, a1 = cut[ex], cut[ex + 1]
-                if a1 > a0:
-                    call('p3_gemm', ptr(xs[a0:a1]), xs.stride(0), ptr(L['gu'][ex]), L['gu'].stride(1), None, ptr(gu[a0:a1]), gu.stride(0),
-                         None, None, a1 - a0, 2 * f.ff, self.W, _lib.EPI_F32, 0, st)
-        else:
-            self.gemm_any(xa, L['gu'], gu, rows=order, row_div=f.top, seg=seg, n_groups=f.experts, M=n)
-        self._ev(ev, 'moe_gemm', 2 * n * 2 * f.ff * self.W, L['gu'].numel() * L['gu'].element_size())
-        call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, n, f.ff, f.limit, TagenexConfig.GLU_ALPHA,
-             None, st)
-        ev = self._ev()
-        if dense:
-            for ex in range(f.experts):
-                a0, a1 = cut[ex], cut[ex + 1]
-                if a1 > a0:
-                    call('p3_gemm', ptr(hid[a0:a1]), hid.stride(0), ptr(L['down'][ex]), L['down'].stride(1), None, ptr(dn[a0:a1]),
-                         dn.stride(0), None, None, a1 - a0, self.W, f.ff, _lib.EPI_F32, 0, st)
-        else:
-            self.gemm_any(hid, L['down'], dn, seg=seg, n_groups=f.experts, M=n)
-        self._ev(ev, 'moe_gemm', 2 * n * f.ff * self.W, L['down'].numel() * L['down'].element_size())
-        call('p3_moe_combine', ptr(dn), dn.stride(0), ptr(where), ptr(wts), f.top, ptr(y), T, self.W, st)
+        glu = lambda gu, hid, n: call('p3_glu_clamped', ptr(gu), gu.stride(0), ptr(hid), hid.stride(0), self.f32, n, f.ff, f.limit,
+                                      TagenexConfig.GLU_ALPHA, None, st)
+        self.experts(L['gu'], L['down'], f, xa, y, T, ids, wts, glu)
