@@ -137,7 +137,7 @@ def forward(cfg, weights, tokens, dtype=torch.float32, trace=None):
     """tokens (one sequence from position 0) -> logits [T, vocab]; trace (a list) gets x after every layer run"""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = cfg['norm']['eps']
-    x0 = w['embed'][torch.as_tensor(tokens, dtype=torch.long)] * cfg['embedding']['scale']
+    x0 = w['embed'][torch.as_tensor(tokens, dtype=torch.long)] * (cfg.get('embedding') or {}).get('scale', 1.0)
     x = x0
     for i, first in layer_runs(cfg):
         if first:

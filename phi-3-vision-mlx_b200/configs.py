@@ -236,9 +236,9 @@ def yarn_frequencies(rot):
 
 
 def tiny_tapalix(width=96, vocab=300, layers=None, loop=(1, 3, 2), eps=1e-5):
-    """A small Tapalix config dict for tests: sizes deliberately unequal between layers (dim != vdim != kv_rank, rot.dims below
-    rot_dim is not used by the design but head counts, ranks and group shapes differ), one layer without a feed-forward, one
-    without expert groups, one without a shared expert."""
+    """A small Tapalix config dict for tests: sizes deliberately unequal between layers (dim != vdim != kv_rank; head counts,
+    ranks and group shapes differ), one layer without a feed-forward, one without expert groups and without a shared expert;
+    layers 1 and 2 run twice."""
     rot = lambda dims, factor=4.0: {'base': 10000.0, 'dims': dims,
                                     'scaling': {'factor': factor, 'original': 64, 'fast': 16.0, 'slow': 2.0}}
     la = lambda heads, dim, rd, vdim, rank, scale=None: {

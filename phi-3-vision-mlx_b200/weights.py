@@ -155,3 +155,58 @@ def random_tagenex_weights(cfg, seed=0, device='cpu'):
             t = rn(shape) / shape[-1] ** 0.5
         w[name] = t.to(torch.bfloat16)
     return w
+
+
+def tapalix_tensor_shapes(cfg):
+    """name -> shape of every tensor of a Tapalix checkpoint; cfg = the config.json dict"""
+    W, V = cfg['width'], cfg['vocab']
+    out = {'embed': (V, W)}
+    if cfg.get('loop'):
+        out['loop.in'] = (W, 2 * W)
+    for i, lc in enumerate(cfg['layers']):
+        p, m = f'l{i}.', lc['mixer']
+        H, d, R = m['heads'], m['dim'], m['kv_rank']
+        dv = m.get('vdim', d)
+        dr = m.get('rot_dim', 0) if lc['type'] == 'latent_attention' else 0
+        out.update({p + 'norm1': (W,), p + 'norm1.b': (W,), p + 'mix.q': (H * (d + dr), W), p + 'mix.dkv': (R + dr, W),
+                    p + 'mix.dkv.norm': (R,), p + 'mix.uk': (H * d, R), p + 'mix.uv': (H * dv, R)})
+        if lc['type'] == 'latent_attention_2':
+            out[p + 'mix.g'] = (H * dv, W)
+        out[p + 'mix.o'] = (W, H * dv)
+        f = lc.get('mlp')
+        if f is None:
+            continue
+        F, E = f['expert']['ff'], f['router']['experts']
+        for e in range(E):
+            out.update({f'{p}mlp.e{e}.gate': (F, W), f'{p}mlp.e{e}.up': (F, W), f'{p}mlp.e{e}.down': (W, F)})
+        out.update({p + 'mlp.router': (E, W), p + 'mlp.correction': (E,)})
+        if f.get('shared'):
+            S = f['shared']['ff']
+            out.update({p + 'mlp.shared.gate': (S, W), p + 'mlp.shared.up': (S, W), p + 'mlp.shared.down': (W, S)})
+    out.update({'final.norm': (W,), 'final.norm.b': (W,), 'head': (V, W)})
+    return out
+
+
+def random_tapalix_weights(cfg, seed=0, device='cpu'):
+    """Seeded bf16 tensors for a Tapalix config dict: matrices N(0, 1/fan_in) (the embedding N(0, 1/width), since the design
+    scales it up again; sublayer output matrices at half that spread so the residual grows slowly), norm gains 1 + 0.1 N, norm
+    biases 0.1 N, router logits of unit spread, choice corrections 0.3 N (large enough to change which experts win)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda s: torch.randn(s, generator=g, device=device, dtype=torch.float32)
+    w = {}
+    for name, shape in tapalix_tensor_shapes(cfg).items():
+        leaf = name.split('.', 1)[1] if name.startswith('l') and name[1].isdigit() else name
+        if leaf.endswith('.b'):
+            t = 0.1 * rn(shape)
+        elif leaf.endswith('norm') or leaf.endswith('norm1'):
+            t = 1.0 + 0.1 * rn(shape)
+        elif leaf == 'mlp.correction':
+            t = 0.3 * rn(shape)
+        elif leaf == 'mlp.router':
+            t = rn(shape) * (3.0 / shape[1] ** 0.5)
+        elif leaf == 'mix.o' or leaf.endswith('.down'):
+            t = 0.5 * rn(shape) / shape[-1] ** 0.5
+        else:
+            t = rn(shape) / shape[-1] ** 0.5
+        w[name] = t.to(torch.bfloat16)
+    return w
