@@ -420,12 +420,13 @@ def test_products_per_head_with_gate(lib, dtype, shape):
     for out_dt in (torch.float32, dtype):
         out = torch.zeros(T, H * N + 4, dtype=out_dt, device=dev)
         m.gemm_any(xd, wd, out, N=N, K=K, ldw=K, batch=(H, K, N * K, N))
-        tol = 1e-4 if out_dt == F32 and dtype == F32 else 0.1
-        assert (out.double().cpu()[:, :H * N].view(T, H, N) - ref).abs().max() < tol
+        exact = out_dt == F32 and dtype == F32                # else: a bf16 result carries 2^-9 of its size
+        near = lambda got, want: bool(((got - want).abs() <= (1e-4 if exact else 0.02 + 0.006 * want.abs())).all())
+        assert near(out.double().cpu()[:, :H * N].view(T, H, N), ref)
         assert float(out[:, H * N:].abs().max()) == 0.0
         m.gemm_any(xd, wd, out, N=N, K=K, ldw=K, batch=(H, K, N * K, N), gate=gd[:, 4:])
         want = ref * torch.sigmoid(gate.double()[:, 4:4 + H * N].view(T, H, N))
-        assert (out.double().cpu()[:, :H * N].view(T, H, N) - want).abs().max() < tol
+        assert near(out.double().cpu()[:, :H * N].view(T, H, N), want)
 
 
 @pytest.mark.parametrize('case', ['random', 'negative', 'no_groups', 'single', 'many'])
