@@ -473,6 +473,72 @@ def _emit(line):
 
 
 # ------------------------------------------------------------------------------------------------ --arch tagenex
+def _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf):
+    """prefill and decode throughput of one engine model (B requests of L prompt tokens; decode at CTX_D tokens of context) and
+    the time of every kernel family with its achieved FLOP/s (prefill) or bytes/s (decode) against the measured peaks.
+    Device-timed with CUDA events after warm-up. -> (prompts, numbers)"""
+    import torch
+    from phi3_b200.engine import Engine
+
+    def timed(fn, n):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, vocab, (L,), generator=g).tolist() for _ in range(B)]
+    eng = Engine(m, B * (CTX_D + 64), B)
+
+    def prefill():
+        eng.step([(i, prompts[i], [L - 1]) for i in range(B)], list(range(B)))
+    ms_pf = timed(prefill, args.steps)
+    m.profile = []
+    prefill()
+    torch.cuda.synchronize()
+    fam = {}
+    for kind, a, b, fl, by in m.profile:
+        f = fam.setdefault(kind, [0.0, 0, 0, 0])
+        f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
+    m.profile = None
+    kern_pf = {k: dict(ms=round(v[0], 3), launches=v[3], tflops=round(v[1] / v[0] / 1e9, 1),
+                       frac_of_measured_bf16=round(v[1] / v[0] / 1e9 / tf, 3)) for k, v in fam.items()}
+    # decode: B sequences at CTX_D tokens of context, one token each per step
+    eng.step([(i, prompts[i][:CTX_D - NEW_D - 8], []) for i in range(B)])
+    tok = [1] * B
+
+    def decode():
+        eng.step([(i, [tok[i]], [0]) for i in range(B)])
+    for _ in range(3):
+        decode()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(NEW_D):
+        decode()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_dec = e0.elapsed_time(e1) / NEW_D
+    m.profile = []
+    decode()
+    torch.cuda.synchronize()
+    fam = {}
+    for kind, a, b, fl, by in m.profile:
+        f = fam.setdefault(kind, [0.0, 0, 0, 0])
+        f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
+    m.profile = None
+    kern_dec = {k: dict(ms=round(v[0], 3), launches=v[3], gbs=round(v[2] / v[0] / 1e6, 1),
+                        frac_of_measured_hbm=round(v[2] / v[0] / 1e6 / hbm, 3)) for k, v in fam.items()}
+    return prompts, dict(prefill_tok_s=round(B * L / ms_pf * 1e3), prefill_ms=round(ms_pf, 2), decode_tok_s=round(B / ms_dec * 1e3),
+                         decode_ms_per_step=round(ms_dec, 3), prefill_kernels=kern_pf, decode_kernels=kern_dec)
+
+
 def _tagenex_cfg(width, heads, kv, dim, ff, layers, window, vocab, moe):
     att = {'type': 'attention', 'mixer': {'heads': heads, 'kv_heads': kv, 'dim': dim, 'vdim': dim, 'scale': dim ** -0.5,
                                           'v_mix': True, 'mask': {'size': window}}}
@@ -522,52 +588,9 @@ def run_tagenex(args):
         B = sz.get('batch', 4)
         cfg = _tagenex_cfg(sz['width'], sz['heads'], sz['kv'], sz['dim'], sz['ff'], sz['layers'], sz['window'], vocab, sz['moe'])
         m = TagenexB200(cfg, weights.random_tagenex_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
-        g = torch.Generator().manual_seed(0)
-        prompts = [torch.randint(0, vocab, (L,), generator=g).tolist() for _ in range(B)]
-        eng = Engine(m, B * (CTX_D + 64), B)
-
-        def prefill():
-            eng.step([(i, prompts[i], [L - 1]) for i in range(B)], list(range(B)))
-        ms_pf = timed(prefill, args.steps)
-        m.profile = []
-        prefill()
-        torch.cuda.synchronize()
-        fam = {}
-        for kind, a, b, fl, by in m.profile:
-            f = fam.setdefault(kind, [0.0, 0, 0, 0])
-            f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
-        m.profile = None
-        kern_pf = {k: dict(ms=round(v[0], 3), launches=v[3], tflops=round(v[1] / v[0] / 1e9, 1),
-                           frac_of_measured_bf16=round(v[1] / v[0] / 1e9 / tf, 3)) for k, v in fam.items()}
-        # decode: B sequences at CTX_D tokens of context, one token each per step
-        eng.step([(i, prompts[i][:CTX_D - NEW_D - 8], []) for i in range(B)])
-        tok = [1] * B
-
-        def decode():
-            eng.step([(i, [tok[i]], [0]) for i in range(B)])
-        for _ in range(3):
-            decode()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(NEW_D):
-            decode()
-        e1.record()
-        torch.cuda.synchronize()
-        ms_dec = e0.elapsed_time(e1) / NEW_D
-        m.profile = []
-        decode()
-        torch.cuda.synchronize()
-        fam = {}
-        for kind, a, b, fl, by in m.profile:
-            f = fam.setdefault(kind, [0.0, 0, 0, 0])
-            f[0] += a.elapsed_time(b); f[1] += fl; f[2] += by; f[3] += 1
-        m.profile = None
-        kern_dec = {k: dict(ms=round(v[0], 3), launches=v[3], gbs=round(v[2] / v[0] / 1e6, 1),
-                            frac_of_measured_hbm=round(v[2] / v[0] / 1e6 / hbm, 3)) for k, v in fam.items()}
-        row = dict(size=sz['name'], batch=B, prompt=L, tagenex=dict(prefill_tok_s=round(B * L / ms_pf * 1e3), prefill_ms=round(ms_pf, 2),
-                   decode_tok_s=round(B / ms_dec * 1e3), decode_ms_per_step=round(ms_dec, 3), prefill_kernels=kern_pf, decode_kernels=kern_dec))
-        del eng, m
+        prompts, nums = _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        row = dict(size=sz['name'], batch=B, prompt=L, tagenex=nums)
+        del m
         torch.cuda.empty_cache()
         if sz['kv'] == sz['heads'] and sz['dim'] == 96 and not sz['moe']:
             # Phi-3 at equal size: same width, heads, head size, feed-forward and depth (full attention instead of a window)
@@ -586,6 +609,7 @@ def run_tagenex(args):
             for _ in range(3):
                 ses.step()
             torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(NEW_D):
                 ses.step()
@@ -603,6 +627,73 @@ def run_tagenex(args):
           'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
 
 
+# ------------------------------------------------------------------------------------------------ --arch tapalix
+def _tapalix_cfg(width, heads, dim, rot, vdim, rank, eff, experts, top, shared, layers, vocab):
+    rotc = {'base': 10000.0, 'dims': rot, 'scaling': {'factor': 4.0, 'original': 4096, 'fast': 32.0, 'slow': 1.0}}
+    la = {'type': 'latent_attention', 'mixer': {'heads': heads, 'dim': dim, 'rot_dim': rot, 'vdim': vdim, 'kv_rank': rank,
+                                                'scale': (dim + rot) ** -0.5, 'rot': rotc}}
+    la2 = {'type': 'latent_attention_2', 'mixer': {'heads': heads, 'dim': dim + rot, 'vdim': vdim, 'kv_rank': rank + rot,
+                                                   'scale': (dim + rot) ** -0.5}}
+    moe = {'kind': 'moe', 'expert': {'ff': eff}, 'router': {'experts': experts, 'top': top, 'scale': 2.0,
+                                                              'groups': {'count': 4, 'keep': 2}}, 'shared': {'ff': shared}}
+    return {'architecture': 'Tapalix', 'vocab': vocab, 'width': width, 'norm': {'eps': 1e-5}, 'embedding': {'scale': width ** 0.5},
+            'layers': [dict(la if i % 2 else la2, mlp=moe) for i in range(layers)],
+            'loop': {'start': 1, 'stop': layers - 1, 'times': 2}, 'logit_scale': 1.0, 'logit_softcap': 30.0}
+
+
+def run_tapalix(args):
+    """Throughput of the Tapalix design on the continuous-batching engine at layer sizes of a real model (random weights, bf16
+    serving mode), beside Tagenex, the closest existing model (same engine, page pool, product kernels and expert path), at equal
+    width, head count, per-head key size, expert sizes and number of layer runs. One JSON line: per size the prefill and decode
+    tok/s of both and, per kernel family, time and achieved FLOP/s (prefill) or bytes/s (decode) against the measured peaks."""
+    import torch
+    import phi3_b200  # noqa: F401
+    from phi3_b200 import weights
+    from phi3_b200.tagenex import TagenexB200
+    from phi3_b200.tapalix import TapalixB200
+    hbm, _ = peaks()
+    tf = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))).get('bf16_tflops', 1590.0) if os.path.exists(
+        os.path.join(ROOT, 'MEASURED_PEAKS.json')) else 1590.0
+    dev = torch.device('cuda:0')
+    # latent rows of 128 numbers run on the tensor-core attention kernels, rows of 256 on the fp32 ones
+    sizes = [dict(name='w2048_h16x(64+32)_r96_e8x1408_L4', width=2048, heads=16, dim=64, rot=32, vdim=64, rank=96, eff=1408, experts=8,
+                  top=2, shared=2816, layers=4),
+             dict(name='w2048_h16x(64+32)_r96_e8x1408_L4_b16', width=2048, heads=16, dim=64, rot=32, vdim=64, rank=96, eff=1408,
+                  experts=8, top=2, shared=2816, layers=4, batch=16),
+             dict(name='w3072_h32x(64+32)_r96_e16x1024_L4', width=3072, heads=32, dim=64, rot=32, vdim=96, rank=96, eff=1024, experts=16,
+                  top=4, shared=2048, layers=4),
+             dict(name='w2048_h16x(128+64)_r192_e8x1408_L4', width=2048, heads=16, dim=128, rot=64, vdim=128, rank=192, eff=1408,
+                  experts=8, top=2, shared=2816, layers=4)]
+    vocab, L, CTX_D, NEW_D = 32064, 2048, 2048, 32
+    out = []
+    for sz in sizes:
+        B = sz.get('batch', 4)
+        cfg = _tapalix_cfg(sz['width'], sz['heads'], sz['dim'], sz['rot'], sz['vdim'], sz['rank'], sz['eff'], sz['experts'], sz['top'],
+                           sz['shared'], sz['layers'], vocab)
+        m = TapalixB200(cfg, weights.random_tapalix_weights(cfg, 0, device=dev), dtype=torch.bfloat16)
+        _, nums = _engine_model_numbers(m, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+        runs = len(m.cfg.runs)
+        row = dict(size=sz['name'], batch=B, prompt=L, layer_runs=runs, tapalix=nums)
+        del m
+        torch.cuda.empty_cache()
+        # Tagenex at equal size: as many layers as Tapalix has layer runs, every layer a mixture of the same experts, grouped-query
+        # attention with as many heads of the same key size, no window shorter than the context
+        d = sz['dim'] + sz['rot']
+        if d <= 128:
+            att = {'type': 'attention', 'mixer': {'heads': sz['heads'], 'kv_heads': max(1, sz['heads'] // 8), 'dim': d, 'vdim': sz['vdim'],
+                                                  'scale': d ** -0.5, 'v_mix': False}}
+            mix = {'kind': 'moe', 'expert': {'ff': sz['eff'], 'limit': 7.0}, 'router': {'experts': sz['experts'], 'top': sz['top']}}
+            tcfg = {'architecture': 'Tagenex', 'vocab': vocab, 'width': sz['width'], 'norm': {'eps': 1e-5},
+                    'layers': [dict(att, mlp=mix) for _ in range(runs)]}
+            tm = TagenexB200(tcfg, weights.random_tagenex_weights(tcfg, 0, device=dev), dtype=torch.bfloat16)
+            _, row['tagenex_equal_size'] = _engine_model_numbers(tm, B, L, CTX_D, NEW_D, vocab, args, hbm, tf)
+            del tm
+            torch.cuda.empty_cache()
+        out.append(row)
+    _emit({"metric": "tapalix_prefill_decode_tok_per_s", 'arch': 'tapalix', 'dtype': 'bf16', 'data': 'synthetic', 'n_gpus': 1,
+          'steps': args.steps, 'warmup': max(3, args.warmup), 'peaks': {'hbm_gbs': hbm, 'bf16_tflops': tf}, 'sizes': out})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -610,8 +701,9 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex'],
-                    help='phi3: the headline workload (default); tagenex: prefill / decode throughput of the Tagenex design')
+    ap.add_argument('--arch', default='phi3', choices=['phi3', 'tagenex', 'tapalix'],
+                    help='phi3: the headline workload (default); tagenex / tapalix: prefill / decode throughput of that design on '
+                         'the continuous-batching engine, beside the closest existing model at equal size')
     args = ap.parse_args()
     if not (args.gpus > 1 and int(os.environ.get('WORLD_SIZE', 1)) == 1):      # the self-launching parent just relays its child
         _claim_stdout()
@@ -619,6 +711,8 @@ def main():
         return run_reference(args)
     if args.arch == 'tagenex':
         return run_tagenex(args)
+    if args.arch == 'tapalix':
+        return run_tapalix(args)
     world = int(os.environ.get('WORLD_SIZE', 1))
     if args.gpus > 1 and world == 1:
         # convenience: self-launch under torchrun when called directly with --gpus N

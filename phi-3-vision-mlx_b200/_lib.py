@@ -108,6 +108,7 @@ def lib():
         if lm_only:
             for name in _STRUCT_ENTRIES:
                 getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
+            L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
             L.p3_last_error.restype = C.c_char_p
             L.p3_version.restype = C.c_int
             _lib = L
@@ -125,6 +126,7 @@ def lib():
         L.p3_trace_count.argtypes, L.p3_trace_count.restype = [], C.c_int
         for name in _STRUCT_ENTRIES:                                                        # (const args*, stream)
             getattr(L, name).argtypes, getattr(L, name).restype = [_p, _p], C.c_int
+        L.p3_attn_window_tile_rows.argtypes, L.p3_attn_window_tile_rows.restype = [_p], C.c_int
         _lib = L
     return _lib
 

@@ -172,7 +172,7 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, i
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------
-// bf16 serving mode, head sizes that tile (dim % 16 == 0, vdim % 8 == 0, both <= 128): the two products run on the tensor cores
+// bf16 serving mode, head sizes that tile (dim % 16 == 0, vdim % 8 == 0, both <= 256): the two products run on the tensor cores
 // (mma.sync m16n8k16, fp32 accumulators). One CTA = up to 64 query rows (4 warps x 16) x one head, key tile = one page. The K and
 // V pages and the tile's penalties travel through a two-stage cp.async ring, so page j + 1 is in flight while page j is
 // multiplied. Scores, mask, penalty (index row - col + 63 into the staged slice), sink and the online softmax stay fp32 in
@@ -180,13 +180,17 @@ __device__ __forceinline__ void stage_rows(bf16* dst, int ld, const bf16* src, i
 // ex2); the weights are rounded to bf16 only as the A operand of P.V, taken straight from the score accumulators. K fragments
 // come by ldmatrix from the row-major page, V by ldmatrix.trans. A page that every row of the tile sees in full (behind the
 // diagonal, inside the window) skips the visibility tests.
-template <int DK, int DN>
-__global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
+template <int DK, int DN, int MINB>
+__global__ void __launch_bounds__(128, MINB) attn_window_prefill_mma_kernel(p3_attn_window_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
-    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, vld = a.v_ld > 0 ? a.v_ld : dv;
+    // blockIdx.z = a block of 8 DN value columns (values wider than that are covered by several CTAs that each form the scores)
+    constexpr bool PARTS = DK > 8;                           // only the wide variant is launched with several column blocks
+    const int vc0 = PARTS ? blockIdx.z * 8 * DN : 0, dv = PARTS ? min(a.vdim - vc0, 8 * DN) : a.vdim, dvs = PARTS ? min(a.vdim, 8 * DN) : a.vdim;
+    const int d = a.dim, ldk = d + 8, ldv = dvs + 8, vld = a.v_ld > 0 ? a.v_ld : a.vdim;
+    const bool v_in_k = a.v_pool == a.k_pool && vld == d && a.n_kv == 1;   // values = leading part of the key rows: staged once
     const int stage_elems = P3_PAGE * (ldk + ldv);           // bf16 elements of one stage: K [64][ldk] then V [64][ldv]
     bf16* kv_s = reinterpret_cast<bf16*>(smraw);
     float* pen_s = reinterpret_cast<float*>(kv_s + 2 * stage_elems);   // [2][128]
@@ -205,11 +209,11 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
     auto stage_page = [&](int pg, int st) {                  // all threads: issue the copies of page pg into stage st
         const int page = bt[pg];
         const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
-        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld;
+        const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld + vc0;
         bf16* Ks = kv_s + st * stage_elems;
         bf16* Vs = Ks + P3_PAGE * ldk;
         stage_rows<2 * DK>(Ks, ldk, kp, kc, tid, d);
-        stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
+        if (!v_in_k) stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
         // penalty at distance (row - col + 63) + dmin, dmin = pos0 - (pg * 64 + 63); plain store, made visible by the barrier
         // that follows the wait for this stage
         const int dist = pos0 - (pg * P3_PAGE + 63) + tid;
@@ -244,7 +248,8 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
         cp_async_wait<1>();                                  // page pg has landed (this thread's copies) ...
         __syncthreads();                                     // ... and everyone else's
         const bf16* Ks = kv_s + st * stage_elems;
-        const bf16* Vs = Ks + P3_PAGE * ldk;
+        const bf16* Vs = v_in_k ? Ks + vc0 : Ks + P3_PAGE * ldk;
+        const int ldvs = v_in_k ? ldk : ldv;
         const float* ps = pen_s + st * 128;
         float s[8][4];
 #pragma unroll
@@ -328,7 +333,7 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
             uint32_t pa[4];
             pa[0] = pack_bf16(s[2 * t][0], s[2 * t][1]); pa[1] = pack_bf16(s[2 * t][2], s[2 * t][3]);
             pa[2] = pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]); pa[3] = pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3]);
-            const bf16* vrow = Vs + (t * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + 8 * (lane >> 4);
+            const bf16* vrow = Vs + (t * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldvs + 8 * (lane >> 4);
 #pragma unroll
             for (int n = 0; n < DN; n += 2) {
                 if (n * 8 < dv) {
@@ -343,7 +348,7 @@ __global__ void __launch_bounds__(128, 3) attn_window_prefill_mma_kernel(p3_attn
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    bf16* out = (bf16*)a.out + (size_t)h * dv;
+    bf16* out = (bf16*)a.out + (size_t)h * a.vdim + vc0;
 #pragma unroll
     for (int half = 0; half < 2; half++) {
         const int row = half ? r1 : r0;
@@ -541,12 +546,17 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 // The loop holds no plain global load on its critical path: the penalties of a page's 64 distances travel with the page
 // (4-byte async copies into the stage), and the block-table entry of the page issued next is read one iteration ahead.
 template <int DK, int DN>
-__global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_window_args a, int n_stages) {
+__global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_window_args a, int n_stages, int v_parts) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) unsigned char smraw[];
     constexpr float LOG2E = 1.4426950408889634f;
-    const int d = a.dim, dv = a.vdim, ldk = d + 8, ldv = dv + 8, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : dv;
+    // blockIdx.y = K/V head x block of 8 DN value columns (wider values: several CTAs that each form the scores)
+    constexpr bool PARTS = DK > 8;                           // only the wide variant is launched with several column blocks
+    if (!PARTS) v_parts = 1;
+    const int vc0 = PARTS ? (blockIdx.y % v_parts) * 8 * DN : 0, dv = PARTS ? min(a.vdim - vc0, 8 * DN) : a.vdim, dvs = PARTS ? min(a.vdim, 8 * DN) : a.vdim;
+    const int d = a.dim, ldk = d + 8, ldv = dvs + 8, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : a.vdim;
+    const bool v_in_k = a.v_pool == a.k_pool && vld == d && G == 1;       // values = leading part of the key rows: staged once
     const int pr = min(rep, 16);                             // penalty rows per stage
     const int stage_bytes = P3_PAGE * (ldk + ldv) * 2 + pr * P3_PAGE * 4;   // K [64][ldk], V [64][ldv] (bf16), penalties [pr][64] (fp32)
     float* Ms = reinterpret_cast<float*>(smraw);             // after the stream: [4 warps][16 rows] maxima, sums, [4][16][dv] vectors
@@ -554,7 +564,7 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
     float* Os = Ls + 64;
     const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
     const int row = tile.x, slot = tile.z, pos = tile.w;
-    const int g = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+    const int g = PARTS ? blockIdx.y / v_parts : blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int pg_first = first / P3_PAGE, pg_last = pos / P3_PAGE;
@@ -569,11 +579,11 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
         const int nr = min(16, rep - h0), hb = g * rep + h0;
         auto stage_page = [&](int pg, int page, int st) {
             const bf16* kp = (const bf16*)a.k_pool + ((size_t)page * G + g) * P3_PAGE * d;
-            const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * vld;
+            const bf16* vp = (const bf16*)a.v_pool + ((size_t)page * G + g) * P3_PAGE * vld + vc0;
             bf16* Ks = reinterpret_cast<bf16*>(smraw + (size_t)st * stage_bytes);
             bf16* Vs = Ks + P3_PAGE * ldk;
             stage_rows<2 * DK>(Ks, ldk, kp, kc, tid, d);
-            stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
+            if (!v_in_k) stage_rows<DN>(Vs, ldv, vp, vc, tid, vld);
             if (a.penalty) {
                 float* Ps = reinterpret_cast<float*>(Vs + P3_PAGE * ldv);
                 for (int i = tid; i < nr * P3_PAGE; i += 128) {
@@ -670,7 +680,8 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
             uint32_t pa[4];
             pa[0] = pack_bf16(s[0][0], s[0][1]); pa[1] = pack_bf16(s[0][2], s[0][3]);
             pa[2] = pack_bf16(s[1][0], s[1][1]); pa[3] = pack_bf16(s[1][2], s[1][3]);
-            const bf16* vrow = Vs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + 8 * (lane >> 4);
+            const bf16* vrow = v_in_k ? Ks + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + 8 * (lane >> 4) + vc0
+                                      : Vs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldv + 8 * (lane >> 4);
 #pragma unroll
             for (int n = 0; n < DN; n += 2) {
                 if (n * 8 < dv) {
@@ -713,11 +724,11 @@ __global__ void __launch_bounds__(128, 2) attn_window_decode_mma_kernel(p3_attn_
             }
             if (n_splits == 1) {
                 const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
-                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * dv + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / L : 0.f);
+                ((bf16*)a.out)[(size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c] = __float2bfloat16_rn(L > 0.f ? acc * gate / L : 0.f);
             } else {
-                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (dv + 2);
-                if (c == 0) { w[0] = M; w[1] = L; }
-                w[2 + c] = acc;
+                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
+                if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
+                w[2 + vc0 + c] = acc;
             }
         }
     }
@@ -803,39 +814,51 @@ int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
 static bool prefill_mma_ok(const p3_attn_window_args* a) {
     static int off = -1;
     if (off < 0) { const char* e = getenv("P3_ATTN_WINDOW_MMA"); off = (e && e[0] == '0') ? 1 : 0; }
-    return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 128 && a->vdim <= 128 &&
+    return !off && !a->act_f32 && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= 256 && a->vdim <= 256 &&
            a->ld_q % 2 == 0 && a->ld_out % 2 == 0 && ((uintptr_t)a->q & 3) == 0 && ((uintptr_t)a->out & 3) == 0 &&
            ((uintptr_t)a->k_pool & 15) == 0 && ((uintptr_t)a->v_pool & 15) == 0 && a->v_ld % 8 == 0;
 }
 
 static int launch_prefill_mma(const p3_attn_window_args* a, cudaStream_t st) {
-    const size_t bytes = 2 * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + 128 * sizeof(float));   // two stages
-    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads);
-    if (a->dim <= 64 && a->vdim <= 64) {
-        if (set_smem(attn_window_prefill_mma_kernel<4, 8>, bytes, "attn_window_prefill")) return -1;
-        p3_launch_pdl(attn_window_prefill_mma_kernel<4, 8>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
+    // key rows above 128 numbers: the <16, 16> variant, values in column blocks of 128 (grid.z), each CTA forms the scores itself
+    const bool wide = a->dim > 128 || a->vdim > 128;
+    const int vcols = wide ? 128 : (a->dim <= 64 && a->vdim <= 64 ? 64 : 128), dvs = a->vdim < vcols ? a->vdim : vcols;
+    const size_t bytes = 2 * (sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + dvs + 8) + 128 * sizeof(float));   // two stages
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads, (unsigned)((a->vdim + vcols - 1) / vcols));
+    if (wide) {
+        if (set_smem(attn_window_prefill_mma_kernel<16, 16, 2>, bytes, "attn_window_prefill")) return -1;
+        p3_launch_pdl(attn_window_prefill_mma_kernel<16, 16, 2>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
+    } else if (a->dim <= 64 && a->vdim <= 64) {
+        if (set_smem(attn_window_prefill_mma_kernel<4, 8, 3>, bytes, "attn_window_prefill")) return -1;
+        p3_launch_pdl(attn_window_prefill_mma_kernel<4, 8, 3>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
     } else {
-        if (set_smem(attn_window_prefill_mma_kernel<8, 16>, bytes, "attn_window_prefill")) return -1;
-        p3_launch_pdl(attn_window_prefill_mma_kernel<8, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
+        if (set_smem(attn_window_prefill_mma_kernel<8, 16, 3>, bytes, "attn_window_prefill")) return -1;
+        p3_launch_pdl(attn_window_prefill_mma_kernel<8, 16, 3>, dim3(grid), dim3(128), (size_t)(bytes), st, *a);
     }
     return 0;
 }
 
 static int launch_decode_mma(const p3_attn_window_args* a, cudaStream_t st) {
     const int rep = a->n_heads / a->n_kv, pr = rep < 16 ? rep : 16;
-    const size_t stage = sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + a->vdim + 8) + sizeof(float) * P3_PAGE * (size_t)pr;
+    const bool wide = a->dim > 128 || a->vdim > 128;
+    const int vcols = wide ? 128 : (a->dim <= 64 && a->vdim <= 64 ? 64 : 128), dvs = a->vdim < vcols ? a->vdim : vcols;
+    const int parts = (a->vdim + vcols - 1) / vcols;
+    const size_t stage = sizeof(bf16) * P3_PAGE * (size_t)(a->dim + 8 + dvs + 8) + sizeof(float) * P3_PAGE * (size_t)pr;
     // as many stages as leave room for two CTAs per SM (227 KB, 1 KB reserved per CTA); the merge buffer fits two stages
     int nst = (int)((227 * 1024 / 2 - 1024) / stage);
     nst = nst < 2 ? 2 : (nst > DEC_MAX_STAGES ? DEC_MAX_STAGES : nst);
     const size_t bytes = nst * stage;
     const int ns = a->n_splits > 1 ? a->n_splits : 1;
-    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
-    if (a->dim <= 64 && a->vdim <= 64) {
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)(a->n_kv * parts), (unsigned)ns);
+    if (wide) {
+        if (set_smem(attn_window_decode_mma_kernel<16, 16>, bytes, "attn_window_decode")) return -1;
+        p3_launch_pdl(attn_window_decode_mma_kernel<16, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst, parts);
+    } else if (a->dim <= 64 && a->vdim <= 64) {
         if (set_smem(attn_window_decode_mma_kernel<4, 8>, bytes, "attn_window_decode")) return -1;
-        p3_launch_pdl(attn_window_decode_mma_kernel<4, 8>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst);
+        p3_launch_pdl(attn_window_decode_mma_kernel<4, 8>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst, parts);
     } else {
         if (set_smem(attn_window_decode_mma_kernel<8, 16>, bytes, "attn_window_decode")) return -1;
-        p3_launch_pdl(attn_window_decode_mma_kernel<8, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst);
+        p3_launch_pdl(attn_window_decode_mma_kernel<8, 16>, dim3(grid), dim3(128), (size_t)(bytes), st, *a, nst, parts);
     }
     if (ns > 1) p3_launch_pdl(attn_window_merge_kernel<bf16>, dim3((unsigned)(a->n_tiles * a->n_heads)), dim3(64), (size_t)(0), st, *a, ns, 1);
     return 0;

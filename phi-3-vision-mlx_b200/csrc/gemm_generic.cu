@@ -175,18 +175,30 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
     OT* out = (OT*)p.out + (size_t)blockIdx.z * p.o_bs;
     const float* gate = p.gate ? p.gate + (size_t)blockIdx.z * p.o_bs : nullptr;
+    // a thread holds pairs of neighbouring columns: one 4- or 8-byte store per pair where the pair is aligned
+    const bool pair_ok = (p.ldo % 2 == 0) && (p.o_bs % 2 == 0) && (((uintptr_t)p.out) % (2 * sizeof(OT)) == 0);
 #pragma unroll
     for (int i = 0; i < 2; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int64_t m = m0 + wm + i * 16 + (lane >> 2) + (e >> 1) * 8;
-                const int n = n0 + wn + j * 8 + (lane & 3) * 2 + (e & 1);
-                if (m < m1 && n < p.N) {
-                    float v = acc[i][j][e] + (bias ? bias[n] : 0.f);
-                    if (gate) v *= 1.0f / (1.0f + expf(-gate[(size_t)m * p.ld_gate + n]));
-                    stf(out + (size_t)m * p.ldo + n, v);
+            for (int hlf = 0; hlf < 2; hlf++) {
+                const int64_t m = m0 + wm + i * 16 + (lane >> 2) + hlf * 8;
+                const int n = n0 + wn + j * 8 + (lane & 3) * 2;
+                if (m >= m1 || n >= p.N) continue;
+                float v0 = acc[i][j][hlf * 2] + (bias ? bias[n] : 0.f);
+                float v1 = (n + 1 < p.N) ? acc[i][j][hlf * 2 + 1] + (bias ? bias[n + 1] : 0.f) : 0.f;
+                if (gate) {
+                    v0 *= 1.0f / (1.0f + expf(-gate[(size_t)m * p.ld_gate + n]));
+                    if (n + 1 < p.N) v1 *= 1.0f / (1.0f + expf(-gate[(size_t)m * p.ld_gate + n + 1]));
+                }
+                OT* o = out + (size_t)m * p.ldo + n;
+                if (pair_ok && n + 1 < p.N) {
+                    if constexpr (sizeof(OT) == 4) *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
+                    else *reinterpret_cast<uint32_t*>(o) = pack_bf16(v0, v1);
+                } else {
+                    stf(o, v0);
+                    if (n + 1 < p.N) stf(o + 1, v1);
                 }
             }
 }

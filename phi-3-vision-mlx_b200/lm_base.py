@@ -17,14 +17,16 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _page_slices(pairs, pages, slots=2 * 148):
+def _page_slices(pairs, pages, slots=2 * 148, merge=0.0):
     """slices of the visible pages per (request, K/V head) for the tensor-core decode attention (two CTAs per SM). Cost model in
     units of the memory latency: a CTA pays one latency to fill its copy ring and half of one per page after that (two pages in
-    flight); equal CTAs run in whole rounds of the resident ones."""
+    flight); equal CTAs run in whole rounds of the resident ones. `merge`: what every further slice adds to the merge kernel, which
+    walks the slices of a head one after the other (it matters when one K/V head serves many query heads: few CTAs, so the model
+    would otherwise cut the keys into very many slices)."""
     best, best_cost = 1, float('inf')
     for ns in range(1, max(1, min(pages, 32)) + 1):
         per = -(-pages // ns)
-        cost = -(-pairs * ns // slots) * (1.0 + per / 2.0)
+        cost = -(-pairs * ns // slots) * (1.0 + per / 2.0) + (merge * ns if ns > 1 else 0.0)
         if cost < best_cost - 1e-9:
             best, best_cost = ns, cost
     return best

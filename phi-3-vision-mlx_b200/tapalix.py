@@ -25,6 +25,8 @@ Precision. dtype=bfloat16 (serving): matrices, activations that feed a matrix pr
 positions, angles, scores, softmax, norms, router, gates and the residual sum are fp32. dtype=float32: everything is fp32 on the
 FMA pipes (no TF32).
 """
+import ctypes as C
+
 import torch
 from . import _lib
 from ._lib import call, call_struct, ptr
@@ -86,8 +88,7 @@ class TapalixB200(PagedLM):
                 L['freq'], L['rot_mag'], L['rot_n'] = torch.tensor(fr, dtype=torch.float64).to(self.dev, torch.float32), float(mag), m.rot.dims
             else:
                 L['freq'], L['rot_mag'], L['rot_n'] = None, 1.0, 0
-            key = R + dr
-            L['mma'] = bool(_lib.ATTN_WINDOW_MMA and not self.f32 and key % 16 == 0 and R % 8 == 0 and key <= 128)
+            L['mma'] = self._attention_tile_rows(H, R + dr, R) == 64
             if f is not None:
                 q = p + 'mlp.'
                 L['gu'] = mat(torch.stack([torch.cat([w[f'{q}e{e}.gate'], w[f'{q}e{e}.up']], 0) for e in range(f.experts)], 0))
@@ -98,6 +99,15 @@ class TapalixB200(PagedLM):
         # query rows per attention tile the engine cuts prompt portions into: 64 when every layer takes the tensor-core prefill
         # kernel (csrc/attention_window.cu), else 32
         self.q_tile = 64 if all(L['mma'] for L in self.layers) else 32
+
+    def _attention_tile_rows(self, H, key, R):
+        """query rows per prefill tile that the attention launch takes for these sizes (64: its tensor-core kernels); asked of the
+        library itself so that the engine's tiles and the kernel's choice cannot disagree"""
+        a = _lib.AttnWindowArgs()
+        a.q = a.out = a.k_pool = a.v_pool = a.block_table = a.tiles = 256              # aligned stand-ins: nothing is launched
+        a.ld_q, a.ld_out, a.n_heads, a.n_kv, a.dim, a.vdim, a.v_ld = H * key, H * R, H, 1, key, R, key
+        a.act_f32 = a.cache_f32 = self.f32
+        return int(_lib.lib().p3_attn_window_tile_rows(C.byref(a)))
 
     # ------------------------------------------------------------------ what the engine asks of a model
     def kv_layout(self):
@@ -204,7 +214,8 @@ class TapalixB200(PagedLM):
             w.tiles, w.n_tiles = ptr(b.dec_tiles), b.n_dec
             span = b.max_pos + 1
             if L['mma']:
-                w.n_splits = _page_slices(b.n_dec, 2 * -(-span // 128) + 1)
+                # one shared K/V head: a request is one CTA per slice (two when the values take two column blocks)
+                w.n_splits = _page_slices(b.n_dec * (-(-R // 128) if key > 128 else 1), 2 * -(-span // 128) + 1, merge=0.4)
             else:
                 w.n_splits = max(1, min(-(-8 * 148 // b.n_dec), -(-span // 128)))
             ws = e(b.n_dec * H * w.n_splits * (R + 2)) if w.n_splits > 1 else None

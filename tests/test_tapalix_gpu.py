@@ -509,13 +509,15 @@ def _latent_attention_case(lib, dtype, H, key, R, n_ctx, hot, scale=1.0, seed=0,
     return outs[0], outs[1], ref
 
 
-@pytest.mark.parametrize('shape', [(3, 28, 20, 32), (4, 64, 48, 64), (20, 128, 96, 64), (2, 200, 152, 32), (9, 112, 96, 32)])
+@pytest.mark.parametrize('shape', [(3, 28, 20, 32), (4, 64, 48, 64), (20, 128, 96, 64), (2, 200, 152, 32), (9, 112, 96, 32),
+                                   (6, 256, 192, 64), (17, 192, 136, 64)])
 @pytest.mark.parametrize('dtype', [F32, B16])
 @pytest.mark.parametrize('n_splits', [1, 3])
 def test_latent_attention_far_keys_page_borders_and_first_tokens(lib, shape, dtype, n_splits):
     """one shared cache row per token serves as key (whole row) and as value (its leading part), for every query head. Probed:
     keys at the very start seen from far away, keys on both sides of page borders, the key at the query's own position, the first
-    positions of a sequence. Shapes cover the fp32 kernels and the tensor-core ones (64- and 128-wide keys, more than 16 heads)."""
+    positions of a sequence. Shapes cover the fp32 kernels and the tensor-core ones (64-, 128- and 256-wide keys, values in one
+    or two column blocks, more than 16 heads)."""
     H, key, R, tile = shape
     n = 300
     hot = [(299, 0), (298, 1), (191, 2), (131, 63), (132, 64), (133, 65), (200, 127), (201, 128), (64, 64), (63, 63), (128, 128),
