@@ -400,8 +400,8 @@ __global__ void residual_layernorm_kernel(float* x, const float* __restrict__ a1
 
 // ---------------------------------------------------------------- latent attention: what follows the fused input projection
 // Grid (token, job group). Jobs of a token: 0 = the latent vector (RMS norm -> cache) with the shared turning key part
-// (rotation -> cache), 1 .. H = the query heads (plain part -> q_plain, turning part rotated -> q_lat), H + 1 .. = slabs of 1024
-// columns of the gated unit. One warp per job.
+// (rotation -> cache), 1 .. H = the query heads (plain part -> q_plain, turning part rotated -> q_lat); one warp per job. The
+// gated unit's columns are then split over all threads of the token's CTAs, four columns per thread where the pitches allow.
 __device__ __forceinline__ void turn_pair(float u, float v, float ang, float mag, float& ou, float& ov) {
     float sn, cs;
     sincosf(ang, &sn, &cs);
@@ -419,9 +419,8 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
     const int slot = a.tok_slot[t], pos = a.tok_pos[t];
     const int page = a.block_table[(size_t)slot * a.bt_stride + pos / P3_PAGE], off = pos % P3_PAGE;
     const int H = a.n_heads, d = a.dim, dr = a.rot_dim, R = a.kv_rank, half = a.rot_n / 2;
-    const int ff_jobs = (a.n_ff + 1023) / 1024;
     const float fpos = (float)pos;
-    for (int job = blockIdx.y * nw + warp; job < 1 + H + ff_jobs; job += gridDim.y * nw) {
+    for (int job = blockIdx.y * nw + warp; job < 1 + H; job += gridDim.y * nw) {
         if (job == 0) {
             const float* c = pr + a.c_off;
             CT* dst = (CT*)a.cache + ((size_t)page * P3_PAGE + off) * (R + dr);
@@ -437,7 +436,7 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
                 stv(dst + R + i, ou); stv(dst + R + half + i, ov);
             }
             for (int i = a.rot_n + lane; i < dr; i += 32) stv(dst + R + i, kr[i]);
-        } else if (job <= H) {
+        } else {
             const int h = job - 1;
             const float* q = pr + a.q_off + (size_t)h * (d + dr);
             AT* qp = (AT*)a.q_plain + (size_t)t * a.ld_qp + (size_t)h * d;
@@ -452,13 +451,25 @@ __global__ void latent_post_kernel(p3_latent_post_args a) {
                 }
                 for (int i = a.rot_n + lane; i < dr; i += 32) stv(ql + i, qr[i]);
             }
-        } else {
-            const int c0 = (job - 1 - H) * 1024, c1 = min(a.n_ff, c0 + 1024);
-            AT* hd = (AT*)a.hid + (size_t)t * a.ld_hid + a.hid_off;
-            for (int i = c0 + lane; i < c1; i += 32) {
-                const float g = pr[a.gate_off + i], u = pr[a.up_off + i];
-                stv(hd + i, g / (1.0f + expf(-g)) * u);
+        }
+    }
+    if (a.n_ff > 0) {
+        const float* g = pr + a.gate_off;
+        const float* u = pr + a.up_off;
+        AT* hd = (AT*)a.hid + (size_t)t * a.ld_hid + a.hid_off;
+        const int n_thr = blockDim.x * gridDim.y, me = blockIdx.y * blockDim.x + threadIdx.x;
+        const bool vec = (a.n_ff % 4 == 0) && (a.gate_off % 4 == 0) && (a.up_off % 4 == 0) && (a.ld_proj % 4 == 0) &&
+                         (a.hid_off % 4 == 0) && (a.ld_hid % 4 == 0) && (((uintptr_t)a.proj & 15) == 0) && (((uintptr_t)a.hid & 15) == 0);
+        if (vec) {
+            for (int i = me * 4; i < a.n_ff; i += n_thr * 4) {
+                const float4 gv = *reinterpret_cast<const float4*>(g + i), uv = *reinterpret_cast<const float4*>(u + i);
+                const float y0 = gv.x / (1.0f + expf(-gv.x)) * uv.x, y1 = gv.y / (1.0f + expf(-gv.y)) * uv.y;
+                const float y2 = gv.z / (1.0f + expf(-gv.z)) * uv.z, y3 = gv.w / (1.0f + expf(-gv.w)) * uv.w;
+                if constexpr (sizeof(AT) == 4) *reinterpret_cast<float4*>(hd + i) = make_float4(y0, y1, y2, y3);
+                else *reinterpret_cast<uint2*>(hd + i) = make_uint2(pack_bf16(y0, y1), pack_bf16(y2, y3));
             }
+        } else {
+            for (int i = me; i < a.n_ff; i += n_thr) { const float gv = g[i]; stv(hd + i, gv / (1.0f + expf(-gv)) * u[i]); }
         }
     }
 }
@@ -474,6 +485,25 @@ __global__ void glu_silu_kernel(const float* __restrict__ g, const float* __rest
         const int64_t r = i / F; const int c = (int)(i % F);
         const float gv = g[(size_t)r * ld + c], uv = u[(size_t)r * ld + c];
         stv(out + (size_t)r * ldo + c, gv / (1.0f + expf(-gv)) * uv);
+    }
+}
+
+// four columns per thread (F, the row pitches and the pointers are multiples of four elements): 16-byte loads
+template <typename AT>
+__global__ void glu_silu_vec4_kernel(const float* __restrict__ g, const float* __restrict__ u, int64_t ld, AT* __restrict__ out,
+                                     int64_t ldo, int64_t R, int F) {
+    pdl_trigger();                                           // the next kernel may set up while this one runs ...
+    pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
+    const int F4 = F / 4;
+    const int64_t n = R * F4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / F4; const int c = (int)(i % F4) * 4;
+        const float4 gv = *reinterpret_cast<const float4*>(g + (size_t)r * ld + c), uv = *reinterpret_cast<const float4*>(u + (size_t)r * ld + c);
+        const float y0 = gv.x / (1.0f + expf(-gv.x)) * uv.x, y1 = gv.y / (1.0f + expf(-gv.y)) * uv.y;
+        const float y2 = gv.z / (1.0f + expf(-gv.z)) * uv.z, y3 = gv.w / (1.0f + expf(-gv.w)) * uv.w;
+        AT* o = out + (size_t)r * ldo + c;
+        if constexpr (sizeof(AT) == 4) *reinterpret_cast<float4*>(o) = make_float4(y0, y1, y2, y3);
+        else *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(y0, y1), pack_bf16(y2, y3));
     }
 }
 
@@ -701,8 +731,10 @@ extern "C" int p3_latent_post(const p3_latent_post_args* a, cudaStream_t st) {
     P3_CHECK_ARG(a->rot_n >= 0 && a->rot_n <= a->rot_dim && a->rot_n % 2 == 0, "latent_post: rot_n must be even and <= rot_dim");
     P3_CHECK_ARG(a->n_ff == 0 || a->hid, "latent_post: the gated unit needs its output");
     if (a->T == 0) return 0;
-    const int jobs = 1 + a->n_heads + (a->n_ff + 1023) / 1024, th = 128;
-    const int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
+    const int jobs = 1 + a->n_heads, th = 128;
+    // few tokens: one warp per job and enough CTAs for the gated unit's columns; many tokens: one CTA per token
+    int groups = a->T >= 1024 ? 1 : (jobs + 3) / 4;
+    if (a->T < 1024 && groups < (a->n_ff + 2047) / 2048) groups = (a->n_ff + 2047) / 2048;
     const dim3 grid((unsigned)a->T, (unsigned)groups);
     if (a->act_f32 && a->cache_f32) p3_launch_pdl(latent_post_kernel<float, float>, dim3(grid), dim3(th), (size_t)(0), st, *a);
     else if (!a->act_f32 && !a->cache_f32) p3_launch_pdl(latent_post_kernel<bf16, bf16>, dim3(grid), dim3(th), (size_t)(0), st, *a);
@@ -714,9 +746,14 @@ extern "C" int p3_latent_post(const p3_latent_post_args* a, cudaStream_t st) {
 extern "C" int p3_glu_silu(const float* g, const float* u, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F,
                            cudaStream_t st) {
     if (R == 0 || F == 0) return 0;
-    const int64_t n = R * F;
+    const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)g & 15) == 0 && ((uintptr_t)u & 15) == 0 &&
+                     ((uintptr_t)out & 15) == 0;
+    const int64_t n = vec ? R * (F / 4) : R * F;
     const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    if (out_f32) p3_launch_pdl(glu_silu_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (float*)out, ldo, R, F);
+    if (vec) {
+        if (out_f32) p3_launch_pdl(glu_silu_vec4_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (float*)out, ldo, R, F);
+        else p3_launch_pdl(glu_silu_vec4_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (bf16*)out, ldo, R, F);
+    } else if (out_f32) p3_launch_pdl(glu_silu_kernel<float>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (float*)out, ldo, R, F);
     else p3_launch_pdl(glu_silu_kernel<bf16>, dim3(grid), dim3(256), (size_t)(0), st, g, u, ld, (bf16*)out, ldo, R, F);
     P3_CHECK_LAUNCH("glu_silu");
     return 0;
