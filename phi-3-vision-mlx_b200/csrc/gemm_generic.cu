@@ -21,7 +21,9 @@ struct AnyP {
     void* out; int64_t ldo;
     int64_t M; int N, K;
     const int32_t* seg; int n_groups;
-    int64_t x_bs, w_bs, o_bs; const float* gate; int64_t ld_gate;     // blockIdx.z = product of a batch (column blocks of X and out)
+    // a batch of nb products over column blocks of X and out: blockIdx.x = m-tile * nb + product, so that the CTAs in flight
+    // together read whole rows of X and write whole rows of out (neighbouring column blocks) instead of one narrow column each
+    int nb; int64_t x_bs, w_bs, o_bs; const float* gate; int64_t ld_gate;
 };
 
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
@@ -51,10 +53,11 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Bs[BK][BN + 4];
     int g; int64_t m0, m1;
-    if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
+    const int bz = blockIdx.x % p.nb;
+    if (!find_tile(p, blockIdx.x / p.nb, g, m0, m1)) return;
     const int n0 = blockIdx.y * BN, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const XT* X = (const XT*)p.X + (size_t)blockIdx.z * p.x_bs;
-    const WT* W = (const WT*)p.W + (size_t)g * p.w_gstride + (size_t)blockIdx.z * p.w_bs;
+    const XT* X = (const XT*)p.X + (size_t)bz * p.x_bs;
+    const WT* W = (const WT*)p.W + (size_t)g * p.w_gstride + (size_t)bz * p.w_bs;
     // this thread stages row (tid / 4) of each tile, k = (tid % 4) * 4 .. + 3
     const int lr = tid >> 2, lk = (tid & 3) * 4;
     const int64_t am = m0 + lr;
@@ -83,8 +86,8 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
         __syncthreads();
     }
     const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
-    OT* out = (OT*)p.out + (size_t)blockIdx.z * p.o_bs;
-    const float* gate = p.gate ? p.gate + (size_t)blockIdx.z * p.o_bs : nullptr;
+    OT* out = (OT*)p.out + (size_t)bz * p.o_bs;
+    const float* gate = p.gate ? p.gate + (size_t)bz * p.o_bs : nullptr;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int64_t m = m0 + ty * 4 + i;
@@ -113,11 +116,12 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     __shared__ __align__(16) bf16 As[BM][TK + 8];
     __shared__ __align__(16) bf16 Bs[BN][TK + 8];
     int g; int64_t m0, m1;
-    if (!find_tile(p, blockIdx.x, g, m0, m1)) return;
+    const int bz = blockIdx.x % p.nb;
+    if (!find_tile(p, blockIdx.x / p.nb, g, m0, m1)) return;
     const int n0 = blockIdx.y * BN, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
-    const bf16* X = (const bf16*)p.X + (size_t)blockIdx.z * p.x_bs;
-    const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride + (size_t)blockIdx.z * p.w_bs;
+    const bf16* X = (const bf16*)p.X + (size_t)bz * p.x_bs;
+    const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride + (size_t)bz * p.w_bs;
     // staging: 64 rows x 16 chunks of 8 elements per operand; round j: row 8 j + 2 warp + lane / 16, chunk lane % 16
     const int srow0 = 2 * warp + (lane >> 4), schunk = (lane & 15) * 8;
     int64_t aoff[8];                                        // element offset of this thread's A row in round j, -1: no such row
@@ -173,8 +177,8 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
         __syncthreads();
     }
     const float* bias = p.bias ? p.bias + (size_t)g * p.bias_gstride : nullptr;
-    OT* out = (OT*)p.out + (size_t)blockIdx.z * p.o_bs;
-    const float* gate = p.gate ? p.gate + (size_t)blockIdx.z * p.o_bs : nullptr;
+    OT* out = (OT*)p.out + (size_t)bz * p.o_bs;
+    const float* gate = p.gate ? p.gate + (size_t)bz * p.o_bs : nullptr;
     // a thread holds pairs of neighbouring columns: one 4- or 8-byte store per pair where the pair is aligned
     const bool pair_ok = (p.ldo % 2 == 0) && (p.o_bs % 2 == 0) && (((uintptr_t)p.out) % (2 * sizeof(OT)) == 0);
 #pragma unroll
@@ -213,12 +217,12 @@ extern "C" int p3_gemm_any(const p3_gemm_any_args* a, cudaStream_t st) {
     if (a->M == 0) return 0;
     AnyP p{a->X, a->ldx, a->x_rows, a->x_row_div, a->W, a->ldw, a->w_group_stride, a->bias, a->bias_group_stride,
            a->out, a->ldo, a->M, a->N, a->K, a->seg_offsets, a->seg_offsets ? a->n_groups : 1,
-           a->x_batch_stride, a->w_batch_stride, a->out_batch_stride, a->gate, a->ld_gate};
-    const int nb = a->n_batch > 1 ? a->n_batch : 1;
+           a->n_batch > 1 ? a->n_batch : 1, a->x_batch_stride, a->w_batch_stride, a->out_batch_stride, a->gate, a->ld_gate};
+    const int nb = p.nb;
     P3_CHECK_ARG(nb <= 65535, "gemm_any: too many products in a batch");
     if (nb == 1) p.x_bs = p.w_bs = p.o_bs = 0;
     const unsigned mt = (unsigned)((a->M + BM - 1) / BM) + (a->seg_offsets ? (unsigned)a->n_groups : 0u);
-    const dim3 grid(mt, (unsigned)((a->N + BN - 1) / BN), (unsigned)nb);
+    const dim3 grid(mt * (unsigned)nb, (unsigned)((a->N + BN - 1) / BN));
     if (a->x_f32) {
         if (a->out_f32) p3_launch_pdl(gemm_any_fma_kernel<float, float, float>, dim3(grid), dim3(256), (size_t)(0), st, p);
         else p3_launch_pdl(gemm_any_fma_kernel<float, float, bf16>, dim3(grid), dim3(256), (size_t)(0), st, p);
