@@ -1,7 +1,8 @@
 // Paged attention over a ragged batch with a sliding window, a per-head sink in the softmax denominator and a per-head distance
 // penalty: score(i, j) = scale * q_i . k_j - pen[h][i - j], visible when 0 <= i - j < window (window 0: every earlier key),
 // weights = exp(score) / (exp(sink_h) + sum over visible exp(score)); optional per-(token, head) output gate. Head sizes of
-// keys (dim) and values (vdim) are independent run-time numbers (<= 256), grouped-query heads share K/V (head h reads h / (H/G)).
+// keys (dim) and values (vdim) are independent run-time numbers, grouped-query heads share K/V (head h reads h / (H/G)). The fp32
+// kernels take any size (rows above 256 numbers in key chunks and value column blocks), the tensor-core kernels sizes up to 256.
 // With no window, sink or penalty this is plain causal attention; with v_pool == k_pool and v_ld == dim the value of a token is
 // the leading part of its key row, which is how a latent-vector cache (one shared "head" that every query head reads, the
 // up-projections folded into the queries and applied to the outputs) is served.
@@ -28,14 +29,18 @@ template <> __device__ __forceinline__ void stv<float>(float* p, float v) { *p =
 template <> __device__ __forceinline__ void stv<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 constexpr int BQ = 32, WARPS = 4, RPW = BQ / WARPS;          // prefill: query rows per CTA / per warp
+constexpr int WIDE = 256;                                    // fp32 kernels: key numbers per chunk, value columns per CTA
 
 template <typename AT, typename CT, int DVC>
 __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn_window_args a) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
-    const int d = a.dim, dv = a.vdim, dp = (d + 3) & ~3;       // q rows padded to float4
-    const int vld = a.v_ld > 0 ? a.v_ld : dv;                // pitch of the value rows in a page
+    // Rows of more than WIDE numbers: the scores are summed over key chunks of WIDE numbers (Q and K chunks restaged per page),
+    // and the values are covered in column blocks of WIDE by blockIdx.z (each CTA forms the scores itself).
+    const int d = a.dim, nchunk = (d + WIDE - 1) / WIDE, dp = (min(d, WIDE) + 3) & ~3;       // q rows padded to float4
+    const int vc0 = blockIdx.z * WIDE, dv = min(a.vdim - vc0, WIDE);
+    const int vld = a.v_ld > 0 ? a.v_ld : a.vdim;            // pitch of the value rows in a page
     float* Qs = sm;                                          // [BQ][dp]
     float* Ks = Qs + BQ * dp;                                // [64][dp + 1]
     float* Vs = Ks + P3_PAGE * (dp + 1);                     // [64][dv]
@@ -45,10 +50,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     const int h = blockIdx.y, g = h / (a.n_heads / a.n_kv);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const AT* q = (const AT*)a.q;
-    for (int i = tid; i < BQ * dp; i += blockDim.x) {
-        const int r = i / dp, c = i % dp;
-        Qs[i] = (r < nq && c < d) ? ldv(q + (size_t)(row0 + r) * a.ld_q + (size_t)h * d + c) * a.scale : 0.f;
-    }
+    auto stage_q = [&](int c0, int dcur) {
+        for (int i = tid; i < BQ * dp; i += blockDim.x) {
+            const int r = i / dp, c = i % dp;
+            Qs[i] = (r < nq && c < dcur) ? ldv(q + (size_t)(row0 + r) * a.ld_q + (size_t)h * d + c0 + c) * a.scale : 0.f;
+        }
+    };
+    if (nchunk == 1) stage_q(0, d);
     const float sink = a.sink ? a.sink[h] : -FLT_MAX;
     float m[RPW], l[RPW], acc[RPW][DVC];
 #pragma unroll
@@ -64,28 +72,33 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
     for (int pg = first / P3_PAGE; pg <= last / P3_PAGE; pg++) {
         const int page = bt[pg];
         const CT* kp = (const CT*)a.k_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * d;
-        const CT* vp = (const CT*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld;
-        __syncthreads();                                     // previous tile fully consumed (and Qs written, first time)
-        for (int i = tid; i < P3_PAGE * d; i += blockDim.x) Ks[(i / d) * (dp + 1) + (i % d)] = ldv(kp + i);
-        for (int i = tid; i < P3_PAGE * dv; i += blockDim.x) Vs[i] = ldv(vp + (size_t)(i / dv) * vld + (i % dv));
-        __syncthreads();
+        const CT* vp = (const CT*)a.v_pool + ((size_t)page * a.n_kv + g) * P3_PAGE * vld + vc0;
         // scores: this warp's RPW rows x keys (lane, lane + 32)
         float s[RPW][2];
 #pragma unroll
         for (int r = 0; r < RPW; r++) s[r][0] = s[r][1] = 0.f;
-        const float* k0 = Ks + lane * (dp + 1);
-        const float* k1 = Ks + (lane + 32) * (dp + 1);
-        for (int i = 0; i < d; i += 4) {
-            float ka[4], kb[4];
+        for (int ck = 0; ck < nchunk; ck++) {
+            const int c0 = ck * WIDE, dcur = min(WIDE, d - c0);
+            __syncthreads();                                 // previous tile / chunk fully consumed (and Qs written, first time)
+            if (nchunk > 1) stage_q(c0, dcur);
+            for (int i = tid; i < P3_PAGE * dcur; i += blockDim.x) Ks[(i / dcur) * (dp + 1) + (i % dcur)] = ldv(kp + (size_t)(i / dcur) * d + c0 + (i % dcur));
+            if (ck == 0)
+                for (int i = tid; i < P3_PAGE * dv; i += blockDim.x) Vs[i] = ldv(vp + (size_t)(i / dv) * vld + (i % dv));
+            __syncthreads();
+            const float* k0 = Ks + lane * (dp + 1);
+            const float* k1 = Ks + (lane + 32) * (dp + 1);
+            for (int i = 0; i < dcur; i += 4) {
+                float ka[4], kb[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) { const bool in = i + e < d; ka[e] = in ? k0[i + e] : 0.f; kb[e] = in ? k1[i + e] : 0.f; }
+                for (int e = 0; e < 4; e++) { const bool in = i + e < dcur; ka[e] = in ? k0[i + e] : 0.f; kb[e] = in ? k1[i + e] : 0.f; }
 #pragma unroll
-            for (int r = 0; r < RPW; r++) {
-                const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp * RPW + r) * dp + i);
-                s[r][0] = fmaf(qv.x, ka[0], s[r][0]); s[r][0] = fmaf(qv.y, ka[1], s[r][0]);
-                s[r][0] = fmaf(qv.z, ka[2], s[r][0]); s[r][0] = fmaf(qv.w, ka[3], s[r][0]);
-                s[r][1] = fmaf(qv.x, kb[0], s[r][1]); s[r][1] = fmaf(qv.y, kb[1], s[r][1]);
-                s[r][1] = fmaf(qv.z, kb[2], s[r][1]); s[r][1] = fmaf(qv.w, kb[3], s[r][1]);
+                for (int r = 0; r < RPW; r++) {
+                    const float4 qv = *reinterpret_cast<const float4*>(Qs + (warp * RPW + r) * dp + i);
+                    s[r][0] = fmaf(qv.x, ka[0], s[r][0]); s[r][0] = fmaf(qv.y, ka[1], s[r][0]);
+                    s[r][0] = fmaf(qv.z, ka[2], s[r][0]); s[r][0] = fmaf(qv.w, ka[3], s[r][0]);
+                    s[r][1] = fmaf(qv.x, kb[0], s[r][1]); s[r][1] = fmaf(qv.y, kb[1], s[r][1]);
+                    s[r][1] = fmaf(qv.z, kb[2], s[r][1]); s[r][1] = fmaf(qv.w, kb[3], s[r][1]);
+                }
             }
         }
         // mask, penalty, online softmax; P goes to shared memory for the P.V pass
@@ -148,7 +161,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_window_prefill_kernel(p3_attn
 #pragma unroll
         for (int j = 0; j < DVC; j++) {
             const int c = lane + 32 * j;
-            if (c < dv) stv(out + (size_t)(row0 + qr) * a.ld_out + (size_t)h * dv + c, acc[r][j] * inv);
+            if (c < dv) stv(out + (size_t)(row0 + qr) * a.ld_out + (size_t)h * a.vdim + vc0 + c, acc[r][j] * inv);
         }
     }
 }
@@ -385,18 +398,20 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f)
 // merged through shared memory; with several slices the CTA writes its unnormalised (max, sum, vector) to the workspace and
 // attn_window_merge_kernel combines them. The sink enters once, as the initial state of slice 0's first warp.
 template <typename AT, typename CT, int DVC>
-__global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_window_args a) {
+__global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_window_args a, int v_parts) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
     extern __shared__ __align__(16) float sm[];
-    const int d = a.dim, dv = a.vdim, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : dv;
+    // blockIdx.y = K/V head x block of WIDE value columns (wider values: several CTAs that each form the scores)
+    const int vc0 = (blockIdx.y % v_parts) * WIDE, dv = min(a.vdim - vc0, WIDE);
+    const int d = a.dim, rep = a.n_heads / a.n_kv, G = a.n_kv, vld = a.v_ld > 0 ? a.v_ld : a.vdim;
     float* Qs = sm;                                          // [RMAX][d]
     float* Ms = Qs + RMAX * d;                               // [DW][RMAX]
     float* Ls = Ms + DW * RMAX;                              // [DW][RMAX]
     float* As = Ls + DW * RMAX;                              // [DW][RMAX][dv]
     const int4 tile = reinterpret_cast<const int4*>(a.tiles)[blockIdx.x];
     const int row = tile.x, slot = tile.z, pos = tile.w;
-    const int g = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+    const int g = blockIdx.y / v_parts, split = blockIdx.z, n_splits = gridDim.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int per = (((pos - first + 1) + n_splits - 1) / n_splits + 31) & ~31;
@@ -468,7 +483,7 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
 #pragma unroll
                 for (int u = 0; u < VR; u++) {
                     const int kp2 = min(kb + k0 + u, k_hi - 1);
-                    const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * vld;
+                    const CT* vp = (const CT*)a.v_pool + (((size_t)bt[kp2 / P3_PAGE] * G + g) * P3_PAGE + kp2 % P3_PAGE) * vld + vc0;
 #pragma unroll
                     for (int j = 0; j < DVC; j++) { const int c = lane + 32 * j; vr[u][j] = c < dv ? ldv(vp + c) : 0.f; }
                 }
@@ -506,11 +521,11 @@ __global__ void __launch_bounds__(DW * 32) attn_window_decode_kernel(p3_attn_win
             }
             if (n_splits == 1) {
                 const float gate = a.gate ? a.gate[(size_t)row * a.n_heads + hb + r] : 1.f;
-                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * dv + c, L > 0.f ? o * gate / L : 0.f);
+                stv((AT*)a.out + (size_t)row * a.ld_out + (size_t)(hb + r) * a.vdim + vc0 + c, L > 0.f ? o * gate / L : 0.f);
             } else {
-                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (dv + 2);
-                if (c == 0) { w[0] = M; w[1] = L; }
-                w[2 + c] = o;
+                float* w = a.ws + (((size_t)blockIdx.x * a.n_heads + hb + r) * n_splits + split) * (a.vdim + 2);
+                if (c == 0 && vc0 == 0) { w[0] = M; w[1] = L; }            // every column block forms the same maximum and sum
+                w[2 + vc0 + c] = o;
             }
         }
     }
@@ -765,7 +780,7 @@ __global__ void attn_window_merge_kernel(p3_attn_window_args a, int n_splits, in
 int check_args(const p3_attn_window_args* a, const char* who) {
     P3_CHECK_ARG(a && a->q && a->k_pool && a->v_pool && a->block_table && a->out && a->tiles, "%s: null argument", who);
     P3_CHECK_ARG(a->n_heads >= 1 && a->n_kv >= 1 && a->n_heads % a->n_kv == 0, "%s: heads must be a multiple of kv heads", who);
-    P3_CHECK_ARG(a->dim >= 1 && a->dim <= 256 && a->vdim >= 1 && a->vdim <= 256, "%s: head sizes must be in [1, 256]", who);
+    P3_CHECK_ARG(a->dim >= 1 && a->dim <= 4096 && a->vdim >= 1 && a->vdim <= 4096, "%s: head sizes must be in [1, 4096]", who);
     P3_CHECK_ARG(!a->penalty || a->n_penalty >= 1, "%s: empty penalty table", who);
     P3_CHECK_ARG(a->act_f32 == a->cache_f32, "%s: activations and cache must both be fp32 or both bf16", who);
     P3_CHECK_ARG(a->v_ld == 0 || a->v_ld >= a->vdim, "%s: the value row pitch must hold a value row", who);
@@ -783,10 +798,10 @@ int set_smem(K kernel, size_t bytes, const char* who) {
 
 template <typename AT, typename CT>
 int launch_prefill(const p3_attn_window_args* a, cudaStream_t st) {
-    const int dp = (a->dim + 3) & ~3;
-    const size_t bytes = sizeof(float) * ((size_t)BQ * dp + (size_t)P3_PAGE * (dp + 1) + (size_t)P3_PAGE * a->vdim + (size_t)BQ * (P3_PAGE + 4));
-    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads);
-    const int c = (a->vdim + 31) / 32;
+    const int dc = a->dim < WIDE ? a->dim : WIDE, dp = (dc + 3) & ~3, dvb = a->vdim < WIDE ? a->vdim : WIDE;
+    const size_t bytes = sizeof(float) * ((size_t)BQ * dp + (size_t)P3_PAGE * (dp + 1) + (size_t)P3_PAGE * dvb + (size_t)BQ * (P3_PAGE + 4));
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_heads, (unsigned)((a->vdim + WIDE - 1) / WIDE));
+    const int c = (dvb + 31) / 32;
 #define GO(N)                                                                                              \
     do { if (set_smem(attn_window_prefill_kernel<AT, CT, N>, bytes, "attn_window_prefill")) return -1;      \
          p3_launch_pdl(attn_window_prefill_kernel<AT, CT, N>, dim3(grid), dim3(WARPS * 32), (size_t)(bytes), st, *a); } while (0)
@@ -797,13 +812,14 @@ int launch_prefill(const p3_attn_window_args* a, cudaStream_t st) {
 
 template <typename AT, typename CT>
 int launch_decode(const p3_attn_window_args* a, cudaStream_t st) {
-    const size_t bytes = sizeof(float) * ((size_t)RMAX * a->dim + 2 * DW * RMAX + (size_t)DW * RMAX * a->vdim);
+    const int dvb = a->vdim < WIDE ? a->vdim : WIDE, parts = (a->vdim + WIDE - 1) / WIDE;
+    const size_t bytes = sizeof(float) * ((size_t)RMAX * a->dim + 2 * DW * RMAX + (size_t)DW * RMAX * dvb);
     const int ns = a->n_splits > 1 ? a->n_splits : 1;
-    const dim3 grid((unsigned)a->n_tiles, (unsigned)a->n_kv, (unsigned)ns);
-    const int cv = (a->vdim + 31) / 32;
+    const dim3 grid((unsigned)a->n_tiles, (unsigned)(a->n_kv * parts), (unsigned)ns);
+    const int cv = (dvb + 31) / 32;
 #define GO(NV)                                                                                             \
     do { if (set_smem(attn_window_decode_kernel<AT, CT, NV>, bytes, "attn_window_decode")) return -1;       \
-         p3_launch_pdl(attn_window_decode_kernel<AT, CT, NV>, dim3(grid), dim3(DW * 32), (size_t)(bytes), st, *a); } while (0)
+         p3_launch_pdl(attn_window_decode_kernel<AT, CT, NV>, dim3(grid), dim3(DW * 32), (size_t)(bytes), st, *a, parts); } while (0)
     if (cv <= 1) GO(1); else if (cv <= 2) GO(2); else if (cv <= 4) GO(4); else GO(8);
 #undef GO
     if (ns > 1) p3_launch_pdl(attn_window_merge_kernel<AT>, dim3((unsigned)(a->n_tiles * a->n_heads)), dim3(64), (size_t)(0), st, *a, ns, 0);

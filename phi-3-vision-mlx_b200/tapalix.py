@@ -60,9 +60,9 @@ class TapalixB200(PagedLM):
             a = p + 'mix.'
             H, d, dr, dv, R = m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank
             L = dict(cfg=lc, norm=f32(w[p + 'norm1']), norm_b=f32(w[p + 'norm1.b']), c_gain=f32(w[a + 'dkv.norm']))
-            if R + dr > 256:
+            if R + dr > 4096:
                 raise NotImplementedError(f'layer {i}: a cache row of kv_rank + rot_dim = {R + dr} numbers; the attention kernels '
-                                          'take at most 256')
+                                          'take at most 4096')
             for name, shape in ((a + 'q', (H * (d + dr), self.W)), (a + 'dkv', (R + dr, self.W)), (a + 'uk', (H * d, R)),
                                 (a + 'uv', (H * dv, R)), (a + 'o', (self.W, H * dv))):
                 if tuple(w[name].shape) != shape:

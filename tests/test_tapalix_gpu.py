@@ -283,6 +283,10 @@ OTHER = {
     'wide': (96, dict(layers=[dict(_la(2, 24, 40, 24, 152, scaling=False, base=500.0), mlp=_moe(24, 6, 1, (2, 1), None)),
                               dict(_la(3, 16, 16, 40, 56, dims=8), mlp=None),
                               dict(_la2(2, 40, 24, 200), mlp=_moe(16, 4, 2, (2, 1), 40))], loop=None)),
+    # nothing is a multiple of 4, let alone 8; cache rows above 256 numbers in the second layer
+    'ragged': (50, dict(layers=[dict(_la(3, 7, 6, 5, 9), mlp=_moe(11, 5, 2, None, 13)),
+                                dict(_la(2, 9, 10, 11, 290), mlp=_moe(7, 6, 3, (3, 2), 9)),
+                                dict(_la2(3, 11, 7, 13), mlp=_moe(9, 4, 1, (2, 1), None))], loop=(1, 3, 2))),
     # a loop of one layer that runs once, in the middle
     'once': (64, dict(layers=[dict(_la2(2, 16, 16, 32), mlp=None), dict(_la(2, 16, 16, 16, 32), mlp=_moe(16, 4, 2, (2, 1), 16)),
                               dict(_la2(2, 16, 16, 32), mlp=_moe(16, 4, 2, None, 16))], loop=(1, 2, 1))),
@@ -294,7 +298,7 @@ OTHER = {
 def test_other_sizes(lib, name, dtype):
     configs, weights, engine, tapalix, paged, O = _mods()
     width, kw = OTHER[name]
-    cfg = configs.tiny_tapalix(width=width, vocab=211, **kw)
+    cfg = configs.tiny_tapalix(width=width, vocab=211 if name != 'ragged' else 101, **kw)
     if name == 'wide':
         cfg['logit_softcap'], cfg['logit_scale'] = 0.0, 1.0
         del cfg['embedding']
@@ -510,14 +514,14 @@ def _latent_attention_case(lib, dtype, H, key, R, n_ctx, hot, scale=1.0, seed=0,
 
 
 @pytest.mark.parametrize('shape', [(3, 28, 20, 32), (4, 64, 48, 64), (20, 128, 96, 64), (2, 200, 152, 32), (9, 112, 96, 32),
-                                   (6, 256, 192, 64), (17, 192, 136, 64)])
+                                   (6, 256, 192, 64), (17, 192, 136, 64), (3, 336, 300, 32), (2, 600, 520, 32)])
 @pytest.mark.parametrize('dtype', [F32, B16])
 @pytest.mark.parametrize('n_splits', [1, 3])
 def test_latent_attention_far_keys_page_borders_and_first_tokens(lib, shape, dtype, n_splits):
     """one shared cache row per token serves as key (whole row) and as value (its leading part), for every query head. Probed:
     keys at the very start seen from far away, keys on both sides of page borders, the key at the query's own position, the first
     positions of a sequence. Shapes cover the fp32 kernels and the tensor-core ones (64-, 128- and 256-wide keys, values in one
-    or two column blocks, more than 16 heads)."""
+    or two column blocks, more than 16 heads) and rows above 256 numbers (key chunks and value column blocks of the fp32 kernels)."""
     H, key, R, tile = shape
     n = 300
     hot = [(299, 0), (298, 1), (191, 2), (131, 63), (132, 64), (133, 65), (200, 127), (201, 128), (64, 64), (63, 63), (128, 128),
