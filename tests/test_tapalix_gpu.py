@@ -322,6 +322,88 @@ def test_small_batches_take_the_weight_streaming_products(lib):
     assert_close(b, ref, B16)
 
 
+def _random_config(rng):
+    """a configuration drawn at random: layer count and order of the two mixers, head counts, plain / turning / value / latent
+    sizes (with and without the tensor-core kernels), rotation constants, feed-forwards with and without groups and shared expert
+    or none at all, the looped block anywhere (or nowhere) with 1 to 3 passes, output constants"""
+    width, vocab = rng.choice([64, 96, 128, 160, 200, 256]), rng.choice([97, 256, 1000])
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        heads, vdim = rng.choice([1, 2, 3, 8, 20]), rng.choice([8, 20, 32, 64])
+        if rng.random() < 0.5:
+            dim, rd = rng.choice([8, 24, 32, 64]), rng.choice([2, 8, 16, 32])
+            rank = rng.choice([16, 40, 64, 96, 112, 240 - rd, 128 - rd])
+            layer = _la(heads, dim, rd, vdim, rank, scale=rng.choice([None, 0.07]), scaling=rng.random() < 0.7,
+                        base=rng.choice([100.0, 10000.0, 1e6]))
+        else:
+            layer = _la2(heads, rng.choice([8, 24, 32, 64]), vdim, rng.choice([16, 40, 64, 128, 200]), scale=rng.choice([None, 0.07]))
+        k = rng.random()
+        if k < 0.2:
+            mlp = None
+        else:
+            groups = rng.choice([None, (1, 1), (2, 1), (2, 2), (4, 2), (4, 3)])
+            per = rng.choice([1, 2, 4])
+            e = per * (groups[0] if groups else rng.choice([1, 3, 5]))
+            top = rng.randint(1, e if not groups else groups[1] * per)
+            mlp = _moe(rng.choice([16, 24, 56]), e, top, groups, rng.choice([None, 24, 64]), scale=rng.choice([1.0, 2.5]))
+        layers.append(dict(layer, mlp=mlp))
+    n = len(layers)
+    loop = None
+    if rng.random() < 0.8:
+        lo = rng.randint(0, n - 1)
+        loop = (lo, rng.randint(lo + 1, n), rng.randint(1, 3))
+    cfg = {'architecture': 'Tapalix', 'vocab': vocab, 'width': width, 'norm': {'eps': rng.choice([1e-5, 1e-6])},
+           'embedding': {'scale': rng.choice([1.0, width ** 0.5])}, 'layers': layers, 'logit_scale': rng.choice([1.0, 0.5, 2.0]),
+           'logit_softcap': rng.choice([0.0, 10.0, 30.0])}
+    if loop:
+        cfg['loop'] = {'start': loop[0], 'stop': loop[1], 'times': loop[2]}
+    return cfg
+
+
+@pytest.mark.parametrize('seed', [11, 12, 13, 14, 15, 16])
+def test_random_configurations_under_random_schedules(lib, seed):
+    """five requests of unequal length through a four-slot engine whose pool holds less than their sum: random portions (down to
+    one token) beside decoded tokens, requests that sit out steps, slots and pages taken over by later requests"""
+    import random
+    configs, weights, engine, tapalix, paged, O = _mods()
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    w = weights.random_tapalix_weights(cfg, seed)
+    lens = {'a': rng.randint(130, 330), 'b': rng.randint(2, 90), 'c': rng.randint(60, 200), 'd': rng.randint(1, 40), 'e': rng.randint(65, 130)}
+    toks = {k: tokens(n, cfg['vocab'], 100 * seed + i) for i, (k, n) in enumerate(lens.items())}
+    ref = {k: O.forward(cfg, w, t, torch.float64) for k, t in toks.items()}
+    for dtype in (F32, B16):
+        model = tapalix.TapalixB200(cfg, w, dtype=dtype)
+        eng = engine.Engine(model, 64 * 12, 4)
+        for p in eng.pool.k:
+            p.fill_(9.0)
+        at, got = {k: 0 for k in toks}, {k: [] for k in toks}
+        waiting, live, srng = list(toks), [], random.Random(seed)
+        while waiting or live:
+            while waiting and len(live) < 4 and sum(-(-lens[k] // 64) for k in live + waiting[:1]) <= eng.pool.n_pages:
+                live.append(waiting.pop(0))
+            entries, end = [], []
+            for k in live:
+                if srng.random() < 0.15 and len(live) > 1:
+                    continue
+                n = 1 if at[k] > 0.6 * lens[k] else min(lens[k] - at[k], srng.choice([1, 1, 2, 3, 17, 64, 65, 130]))
+                entries.append((k, toks[k][at[k]:at[k] + n], list(range(n))))
+                at[k] += n
+                if at[k] == lens[k]:
+                    end.append(k)
+            if not entries:
+                continue
+            lg = eng.step(entries, end)
+            o = 0
+            for k, t, wnt in entries:
+                got[k].append(lg[o:o + len(wnt)])
+                o += len(wnt)
+            live = [k for k in live if k not in end]
+        for k in toks:
+            assert_close(torch.cat(got[k], 0), ref[k], dtype, (seed, k, cfg))
+        assert len(eng.pool.free_pages) == eng.pool.n_pages and len(eng.pool.free_slots) == 4
+
+
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 def test_residual_sum_and_layer_norm(lib):
     configs, weights, engine, tapalix, paged, O = _mods()
