@@ -439,12 +439,14 @@ int p3_latent_post(const p3_latent_post_args* args, cudaStream_t st);
 /* out (act) [R, F] = silu(g[r][c]) * u[r][c]; g and u fp32 with the common row pitch ld */
 int p3_glu_silu(const float* g, const float* u, int64_t ld, void* out, int64_t ldo, int out_f32, int64_t R, int F, cudaStream_t st);
 
-/* router with sigmoid scores: z = Wr x (fp32), s = sigmoid(z), choice = s + correction (correction fp32 [E] or NULL). The E
+/* router with sigmoid scores: z = Wr x (fp32; or logits fp32 [T, ld_logits] when an earlier product already formed them with fp32
+ * accumulation: x and Wr are then unused), s = sigmoid(z), choice = s + correction (correction fp32 [E] or NULL). The E
  * experts form n_groups equal groups of neighbours (n_groups <= 1: no groups); a group's score is the sum of its two largest
  * choice scores and only experts of the `keep` best groups can be chosen. ids [T, top] = the `top` largest choice scores among
  * those (ties: lower index); wts = s[ids] / (sum of them + 1e-20) * scale. */
-int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction, int T, int W, int E,
-                             int top, int n_groups, int keep, float scale, int32_t* ids, float* wts, cudaStream_t st);
+int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction, const float* logits,
+                             int64_t ld_logits, int T, int W, int E, int top, int n_groups, int keep, float scale, int32_t* ids,
+                             float* wts, cudaStream_t st);
 
 /* logits <- cap * tanh(logits * scale / cap) (cap <= 0: logits * scale), n numbers in place */
 int p3_logit_softcap(float* logits, int64_t n, float scale, float cap, cudaStream_t st);

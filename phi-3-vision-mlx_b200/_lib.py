@@ -75,7 +75,7 @@ _SIGS = {
     # single-norm parallel layers, latent-vector attention, sigmoid group routing (csrc/seq_ops.cu)
     'p3_residual_layernorm': [_p, _p, _l, _p, _l, _p, _p, _p, _p, _l, _p, _l, _i, _l, _i, _f, _p],
     'p3_glu_silu': [_p, _p, _l, _p, _l, _i, _l, _i, _p],
-    'p3_router_sigmoid_groups': [_p, _l, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p],
+    'p3_router_sigmoid_groups': [_p, _l, _i, _p, _p, _p, _l, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p],
     'p3_logit_softcap': [_p, _l, _f, _f, _p],
 }
 _STRUCT_ENTRIES = ['p3_gemm_any', 'p3_qkv_post', 'p3_attn_window_prefill', 'p3_attn_window_decode', 'p3_latent_post']

@@ -108,8 +108,9 @@ __global__ void __launch_bounds__(256) gemm_any_fma_kernel(AnyP p) {
 // required by the launcher). Same tile walk, gather and segment logic as the FMA kernel. A k-slab is 128 elements: 16 lanes read
 // the 256 contiguous bytes of one row, so that with few rows, where the kernel is a stream of W, DRAM sees bursts instead of
 // 64-byte pieces of 64 rows; the next slab's loads are in flight while this one is multiplied.
-constexpr int TK = 128;                                    // k elements per stage
-template <typename OT>
+// TK = k elements per stage: 128, or 64 for products with K <= 64 (the per-head products of an attention mixer), which would
+// otherwise multiply a half-empty slab and hold twice the staging registers.
+template <typename OT, int TK>
 __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
@@ -122,33 +123,35 @@ __global__ void __launch_bounds__(128) gemm_any_mma_kernel(AnyP p) {
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
     const bf16* X = (const bf16*)p.X + (size_t)bz * p.x_bs;
     const bf16* W = (const bf16*)p.W + (size_t)g * p.w_gstride + (size_t)bz * p.w_bs;
-    // staging: 64 rows x 16 chunks of 8 elements per operand; round j: row 8 j + 2 warp + lane / 16, chunk lane % 16
-    const int srow0 = 2 * warp + (lane >> 4), schunk = (lane & 15) * 8;
-    int64_t aoff[8];                                        // element offset of this thread's A row in round j, -1: no such row
+    // staging: 64 rows x TK / 8 chunks of 8 elements per operand; LPR lanes per row, RPR rows per round of the CTA, NR rounds;
+    // round j: row RPR j + (32 / LPR) warp + lane / LPR, chunk lane % LPR
+    constexpr int LPR = TK / 8, RPR = 128 / LPR, NR = BM / RPR;
+    const int srow0 = (32 / LPR) * warp + lane / LPR, schunk = (lane % LPR) * 8;
+    int64_t aoff[NR];                                       // element offset of this thread's A row in round j, -1: no such row
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const int64_t am = m0 + srow0 + 8 * j;
+    for (int j = 0; j < NR; j++) {
+        const int64_t am = m0 + srow0 + RPR * j;
         aoff[j] = (am < m1) ? (int64_t)(p.x_rows ? p.x_rows[am] / p.x_row_div : am) * p.ldx : -1;
     }
     const bf16* brow0 = W + (size_t)(n0 + srow0) * p.ldw;
     float acc[2][4][4] = {};
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    uint4 ra[8], rb[8];
+    uint4 ra[NR], rb[NR];
     auto fetch = [&](int k0) {
         const int k = k0 + schunk;
         const bool in = k < p.K;                           // K % 8 == 0: a chunk is inside or outside as a whole
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+        for (int j = 0; j < NR; j++) {
             ra[j] = (aoff[j] >= 0 && in) ? __ldg(reinterpret_cast<const uint4*>(X + aoff[j] + k)) : zero;
-            rb[j] = (n0 + srow0 + 8 * j < p.N && in) ? ldg_nc_v4(brow0 + (size_t)(8 * j) * p.ldw + k) : zero;
+            rb[j] = (n0 + srow0 + RPR * j < p.N && in) ? ldg_nc_v4(brow0 + (size_t)(RPR * j) * p.ldw + k) : zero;
         }
     };
     fetch(0);
     for (int k0 = 0; k0 < p.K; k0 += TK) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            *reinterpret_cast<uint4*>(&As[srow0 + 8 * j][schunk]) = ra[j];
-            *reinterpret_cast<uint4*>(&Bs[srow0 + 8 * j][schunk]) = rb[j];
+        for (int j = 0; j < NR; j++) {
+            *reinterpret_cast<uint4*>(&As[srow0 + RPR * j][schunk]) = ra[j];
+            *reinterpret_cast<uint4*>(&Bs[srow0 + RPR * j][schunk]) = rb[j];
         }
         __syncthreads();
         if (k0 + TK < p.K) fetch(k0 + TK);
@@ -231,8 +234,11 @@ extern "C" int p3_gemm_any(const p3_gemm_any_args* a, cudaStream_t st) {
                         (nb == 1 || (a->x_batch_stride % 8 == 0 && a->w_batch_stride % 8 == 0)) &&
                         ((uintptr_t)a->X & 15) == 0 && ((uintptr_t)a->W & 15) == 0 && !a->force_fma;
         if (tc) {
-            if (a->out_f32) p3_launch_pdl(gemm_any_mma_kernel<float>, dim3(grid), dim3(128), (size_t)(0), st, p);
-            else p3_launch_pdl(gemm_any_mma_kernel<bf16>, dim3(grid), dim3(128), (size_t)(0), st, p);
+            if (a->K <= 64) {
+                if (a->out_f32) p3_launch_pdl(gemm_any_mma_kernel<float, 64>, dim3(grid), dim3(128), (size_t)(0), st, p);
+                else p3_launch_pdl(gemm_any_mma_kernel<bf16, 64>, dim3(grid), dim3(128), (size_t)(0), st, p);
+            } else if (a->out_f32) p3_launch_pdl(gemm_any_mma_kernel<float, 128>, dim3(grid), dim3(128), (size_t)(0), st, p);
+            else p3_launch_pdl(gemm_any_mma_kernel<bf16, 128>, dim3(grid), dim3(128), (size_t)(0), st, p);
         } else {
             if (a->out_f32) p3_launch_pdl(gemm_any_fma_kernel<bf16, bf16, float>, dim3(grid), dim3(256), (size_t)(0), st, p);
             else p3_launch_pdl(gemm_any_fma_kernel<bf16, bf16, bf16>, dim3(grid), dim3(256), (size_t)(0), st, p);

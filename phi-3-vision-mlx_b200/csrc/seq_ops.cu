@@ -522,7 +522,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 
 template <typename AT>
 __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t ldx, const float* __restrict__ Wr,
-                                             const float* __restrict__ corr, int W, int E, int top, int n_groups, int keep,
+                                             const float* __restrict__ corr, const float* __restrict__ logits, int64_t ld_logits,
+                                             int W, int E, int top, int n_groups, int keep,
                                              float scale, int32_t* __restrict__ ids, float* __restrict__ wts) {
     pdl_trigger();                                           // the next kernel may set up while this one runs ...
     pdl_wait();                                              // ... and this one touches memory only after its predecessors are done
@@ -533,6 +534,14 @@ __global__ void router_sigmoid_groups_kernel(const AT* __restrict__ x, int64_t l
     float* gsc = ch + E;
     float* part = gsc + NG;
     const AT* xr = x + (size_t)t * ldx;
+    if (logits) {                                            // the logits came out of an earlier product (fp32 accumulation)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            const float sg = 1.0f / (1.0f + expf(-logits[(size_t)t * ld_logits + e]));
+            z[e] = sg;
+            ch[e] = sg + (corr ? corr[e] : 0.f);
+        }
+        __syncthreads();
+    } else
     for (int e0 = 0; e0 < E; e0 += 8) {
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const int ne = min(8, E - e0);
@@ -759,17 +768,19 @@ extern "C" int p3_glu_silu(const float* g, const float* u, int64_t ld, void* out
     return 0;
 }
 
-extern "C" int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction, int T, int W,
-                                        int E, int top, int n_groups, int keep, float scale, int32_t* ids, float* wts, cudaStream_t st) {
+extern "C" int p3_router_sigmoid_groups(const void* x, int64_t ldx, int x_f32, const float* Wr, const float* correction,
+                                        const float* logits, int64_t ld_logits, int T, int W, int E, int top, int n_groups, int keep,
+                                        float scale, int32_t* ids, float* wts, cudaStream_t st) {
+    P3_CHECK_ARG(logits || (x && Wr), "router_sigmoid_groups: needs the logits, or the activations and the router matrix");
     P3_CHECK_ARG(top >= 1 && top <= E && E <= 1024, "router_sigmoid_groups: need 1 <= top <= experts <= 1024");
     const int NG = n_groups > 1 ? n_groups : 1;
     P3_CHECK_ARG(E % NG == 0 && (NG == 1 || (keep >= 1 && keep <= NG && keep * (E / NG) >= top)),
                  "router_sigmoid_groups: groups must divide the experts and the kept groups must hold `top` experts");
     if (T == 0) return 0;
-    const int nw = W >= 1024 ? 8 : 4;
+    const int nw = logits ? 1 : (W >= 1024 ? 8 : 4);         // with ready logits one warp per token does everything
     const size_t sm = ((size_t)2 * E + NG + nw * 8) * sizeof(float);
-    if (x_f32) p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, correction, W, E, top, NG, keep, scale, ids, wts);
-    else p3_launch_pdl(router_sigmoid_groups_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, correction, W, E, top, NG, keep, scale, ids, wts);
+    if (x_f32) p3_launch_pdl(router_sigmoid_groups_kernel<float>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const float*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, ids, wts);
+    else p3_launch_pdl(router_sigmoid_groups_kernel<bf16>, dim3((unsigned)T), dim3(nw * 32), (size_t)(sm), st, (const bf16*)x, ldx, Wr, correction, logits, ld_logits, W, E, top, NG, keep, scale, ids, wts);
     P3_CHECK_LAUNCH("router_sigmoid_groups");
     return 0;
 }

@@ -16,7 +16,7 @@ head (key = the whole row, value = its leading kv_rank numbers: p3_attn_window_*
 up-projection is applied to the attention output. Both per-head products are one batched launch of p3_gemm_any.
 
 Kernels per layer run (csrc/): p3_residual_layernorm (adds the previous run's sublayer outputs to x, norms) -> ONE product for
-q | latent | output-gate logits | shared expert gate, up -> p3_latent_post (latent RMS norm, rotation, cache write, plain query
+q | latent | output-gate logits | shared expert gate, up | router logits -> p3_latent_post (latent RMS norm, rotation, cache write, plain query
 parts, shared expert activation) -> per-head query absorption -> p3_attn_window_prefill / _decode -> per-head value up-projection
 (x sigmoid gate) -> ONE product with [W_o | W_down of the shared expert] over [heads | shared hidden] -> routed experts:
 p3_router_sigmoid_groups -> p3_moe_sort -> grouped gate|up product -> p3_glu_silu -> grouped down product -> p3_moe_combine.
@@ -67,7 +67,7 @@ class TapalixB200(PagedLM):
                                 (a + 'uv', (H * dv, R)), (a + 'o', (self.W, H * dv))):
                 if tuple(w[name].shape) != shape:
                     raise ValueError(f'{name}: shape {tuple(w[name].shape)}, the config gives {shape}')
-            # fused input projection: q | latent and shared turning key | gate logits | shared expert gate | shared expert up
+            # fused input projection: q | latent and shared turning key | gate logits | shared expert gate | shared expert up | router
             parts, off = [w[a + 'q'], w[a + 'dkv']], H * (d + dr) + R + dr
             L['q_off'], L['c_off'] = 0, H * (d + dr)
             L['g_off'] = L['sg_off'] = L['su_off'] = 0
@@ -80,6 +80,14 @@ class TapalixB200(PagedLM):
                 L['sg_off'], L['su_off'] = off, off + sff
                 parts += [w[p + 'mlp.shared.gate'], w[p + 'mlp.shared.up']]
                 off += 2 * sff
+            if f is not None:
+                # the router's rows ride in the same product (fp32 accumulation of exact bf16 products; all-fp32 in the fp32 mode),
+                # padded with zero rows to a multiple of 16 so that small batches keep the weight-streaming kernel
+                L['r_off'] = off
+                pad = -f.experts % 16
+                rw = w[p + 'mlp.router']
+                parts += [rw] + ([torch.zeros(pad, self.W, dtype=rw.dtype, device=rw.device)] if pad else [])
+                off += f.experts + pad
             L['in_w'], L['n_in'] = mat(torch.cat(parts, 0)), off
             # the key up-projection is folded into the query: per head [kv_rank, dim]; the value up-projection stays [vdim, kv_rank]
             L['uk_t'] = mat(w[a + 'uk'].view(H, d, R).transpose(1, 2))
@@ -96,7 +104,6 @@ class TapalixB200(PagedLM):
                 q = p + 'mlp.'
                 L['gu'] = mat(torch.stack([torch.cat([w[f'{q}e{e}.gate'], w[f'{q}e{e}.up']], 0) for e in range(f.experts)], 0))
                 L['down'] = mat(torch.stack([w[f'{q}e{e}.down'] for e in range(f.experts)], 0))
-                L['router'] = f32(w[q + 'router'])
                 L['correction'] = f32(w[q + 'correction']) if (q + 'correction') in w else None
             self.layers.append(L)
         # query rows per attention tile the engine cuts prompt portions into: 64 when every layer takes the tensor-core prefill
@@ -239,8 +246,8 @@ class TapalixB200(PagedLM):
         y_ff = e(T, W)
         ids = torch.empty((T, f.top), dtype=torch.int32, device=dev)
         wts = torch.empty((T, f.top), dtype=torch.float32, device=dev)
-        call('p3_router_sigmoid_groups', ptr(h), h.stride(0), self.f32, ptr(L['router']), ptr(L['correction']), T, W, f.experts,
-             f.top, f.groups, f.keep, f.scale, ptr(ids), ptr(wts), st)
+        call('p3_router_sigmoid_groups', None, 0, self.f32, None, ptr(L['correction']), ptr(proj[:, L['r_off']:]), proj.stride(0),
+             T, W, f.experts, f.top, f.groups, f.keep, f.scale, ptr(ids), ptr(wts), st)
         glu = lambda gu, hd, n: call('p3_glu_silu', ptr(gu), ptr(gu[:, f.ff:]), gu.stride(0), ptr(hd), hd.stride(0), self.f32, n,
                                      f.ff, st)
         self.experts(L['gu'], L['down'], f, h, y_ff, T, ids, wts, glu)

@@ -534,11 +534,18 @@ def test_router_sigmoid_scores_correction_and_groups(lib, case):
     xd, wd, cd = x.to(dev), Wr.to(dev), corr.to(dev)
     ids = torch.empty(T, top, dtype=torch.int32, device=dev)
     wts = torch.empty(T, top, device=dev)
-    call('p3_router_sigmoid_groups', ptr(xd), W, 1, ptr(wd), ptr(cd), T, W, E, top, groups, keep, 2.5, ptr(ids), ptr(wts), 0)
-    got = {(t, int(e)): float(v) for t in range(T) for e, v in zip(ids[t].cpu(), wts[t].cpu())}
     ref = {(t, int(e)): float(v) for t in range(T) for e, v in zip(ids_ref[t], wts_ref[t])}
-    assert got.keys() == ref.keys()
-    assert max(abs(got[k] - ref[k]) for k in ref) < 1e-5
+    logits = torch.zeros(T, E + 3, device=dev)
+    logits[:, :E] = (x.double() @ Wr.double().T).float().to(dev)
+    for from_logits in (False, True):                         # the kernel forms the logits itself, or takes them from a product
+        ids.zero_(), wts.zero_()
+        if from_logits:
+            call('p3_router_sigmoid_groups', None, 0, 1, None, ptr(cd), ptr(logits), E + 3, T, W, E, top, groups, keep, 2.5, ptr(ids), ptr(wts), 0)
+        else:
+            call('p3_router_sigmoid_groups', ptr(xd), W, 1, ptr(wd), ptr(cd), None, 0, T, W, E, top, groups, keep, 2.5, ptr(ids), ptr(wts), 0)
+        got = {(t, int(e)): float(v) for t in range(T) for e, v in zip(ids[t].cpu(), wts[t].cpu())}
+        assert got.keys() == ref.keys()
+        assert max(abs(got[k] - ref[k]) for k in ref) < 1e-5
     assert abs(float(wts.sum(-1).mean()) - 2.5) < 1e-4        # weights sum to the router scale, not to 1
     if groups > 1:
         assert all(len({int(e) // (E // groups) for e in ids[t].cpu()}) <= keep for t in range(T))
