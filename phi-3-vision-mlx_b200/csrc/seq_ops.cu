@@ -373,12 +373,6 @@ __global__ void residual_layernorm_kernel(float* x, const float* __restrict__ a1
     for (int k = 0; k < RPT; k++) { const int i = threadIdx.x + k * nt; v[k] = i < W ? val(i) : 0.f; s += v[k]; }
     for (int i = threadIdx.x + RPT * nt; i < W; i += nt) s += val(i);
     const bool store_x = !rows && (p1 || p2);
-    float gv[RPT], bv[RPT];                                  // weight and bias travel while the statistics are reduced
-#pragma unroll
-    for (int k = 0; k < RPT; k++) {
-        const int i = threadIdx.x + k * nt;
-        gv[k] = (ho && i < W) ? gain[i] : 0.f; bv[k] = (ho && i < W) ? bias[i] : 0.f;
-    }
     float mean = 0.f, rstd = 0.f;
     if (ho) {
         mean = block_sum(s, sh) / (float)W;
@@ -394,7 +388,7 @@ __global__ void residual_layernorm_kernel(float* x, const float* __restrict__ a1
         if (i >= W) continue;
         if (store_x) xr[i] = v[k];
         if (xa) stv(xa + (size_t)r * ldxa + i, v[k]);
-        if (ho) stv(ho + (size_t)r * ldh + i, (v[k] - mean) * rstd * gv[k] + bv[k]);
+        if (ho) stv(ho + (size_t)r * ldh + i, (v[k] - mean) * rstd * gain[i] + bias[i]);
     }
     for (int i = threadIdx.x + RPT * nt; i < W; i += nt) {
         const float u = val(i);
